@@ -3,7 +3,7 @@
 
   distributed-llama-multiusers_b200/lib/libdllama_b200_cuda.so   nvcc, sm_100a only: the Q40 / f32 Llama kernels
   distributed-llama-multiusers_b200/lib/libdllama_b200_layers.so nvcc, sm_100a only: the kernels of layer-list models
-                                                                 (dense bf16 / f32 weights, latent attention, Mamba-2)
+                                                                 (dense bf16 / f32 weights, latent, windowed and linear attention, Mamba-2)
   distributed-llama-multiusers_b200/lib/libdllama_b200_host.so   g++, CPU runtime (tokenizer,
                                                                  sampler, codecs, scheduler ...)
 
@@ -63,7 +63,7 @@ def _run(cmd, verbose, log_path=None):
 
 # sources of the layer-list model library; prep.cu (error plumbing, argmax), sampler.cu and gemm_wh_tc.cu (the tcgen05
 # GEMM on pre-tiled operands) are shared with the other one (their objects are compiled once), the rest is its own
-LAYERS_OWN = ["dense.cu", "hyper.cu", "latent_attention.cu", "mamba2.cu", "moe.cu", "norms.cu", "window_attention.cu"]
+LAYERS_OWN = ["dense.cu", "hyper.cu", "latent_attention.cu", "lightning.cu", "mamba2.cu", "moe.cu", "norms.cu", "window_attention.cu"]
 LAYERS_SHARED = ["gemm_wh_tc.cu", "prep.cu", "sampler.cu"]
 
 

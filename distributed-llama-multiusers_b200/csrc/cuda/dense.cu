@@ -6,7 +6,7 @@
 // load, so products are exact in f32 and only the accumulation order differs from a tensor-core product.
 //
 // Epilogues (what other models of this library fuse into their matmul kernels too): plain store, relu(.)^2,
-// aux * sigmoid(.) (an output gate), cap * tanh(. / cap) (logit soft-capping).
+// aux * sigmoid(.) (an output gate), cap * tanh(. / cap) (logit soft-capping), . * sigmoid(.) (SiLU).
 #include "layer_common.cuh"
 #include "../../../include/dllama_b200.h"
 
@@ -15,6 +15,7 @@ __device__ __forceinline__ float dense_epi(float acc, int epi, float aux, float 
         case DL_DENSE_RELU2: { const float r = fmaxf(acc, 0.f); return r * r; }
         case DL_DENSE_SIGMOID_MUL: return aux * sigmoid_f(acc);
         case DL_DENSE_SOFTCAP: return param * tanhf(acc / param);
+        case DL_DENSE_SILU: return silu_f(acc);
         default: return acc;
     }
 }
@@ -225,6 +226,7 @@ extern "C" int dl_dense(const DlDenseArgs* args, void* stream) {
     const DlDenseArgs& a = *args;
     if (a.M < 1 || a.N < 1 || a.K < 1 || a.batch < 1) { dl_set_error("dl_dense: empty problem"); return -1; }
     if (a.epi == DL_DENSE_SIGMOID_MUL && a.aux == nullptr) { dl_set_error("dl_dense: the gate epilogue needs aux"); return -1; }
+    if (a.epi == DL_DENSE_GLU_CLAMP) { dl_set_error("dl_dense: the paired-column epilogue belongs to the tensor-core GEMM"); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     if (a.wtype == DL_T_BF16) {
         if (a.round_x) launch_dense<__nv_bfloat16, true>(a, st);

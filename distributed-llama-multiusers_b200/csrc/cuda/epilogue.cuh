@@ -175,7 +175,23 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
         }
     } else if (e.kind == DL_EPI_DENSE) {
         // dense-weight models: an element-wise op on the f32 result, then a plain store (one destination)
-        if (tid < rows) {
+        if (e.dense_op == DL_DENSE_GLU_CLAMP) {
+            // output rows interleaved (gate_j, up_j): thread j < rows/2 owns value j of the tile and stores column
+            // grow0 / 2 + j:  g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+            const int col = (grow0 >> 1) + tid;
+            if (tid < (rows >> 1) && 2 * col + 1 < d_real) {
+                const size_t ld = (size_t)e.ld;
+                float* d0 = e.dst[0] + (size_t)e.dst_off + (size_t)m0 * ld + col;
+                const float lim = e.dense_param;
+#pragma unroll 4
+                for (int m = m_first; m < M; m += m_step) {
+                    const float2 gu = *reinterpret_cast<const float2*>(out_s + m * out_ld + 2 * tid);
+                    float g = gu.x, u = gu.y;
+                    if (lim > 0.0f) { g = fminf(g, lim); u = fminf(fmaxf(u, -lim), lim); }
+                    d0[m * ld] = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+                }
+            }
+        } else if (tid < rows) {
             const int grow = grow0 + tid;
             if (grow < d_real) {
                 const size_t ld = (size_t)e.ld, ald = (size_t)e.dense_aux_ld;
@@ -189,6 +205,7 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
                     if (op == DL_DENSE_RELU2) { v = fmaxf(v, 0.0f); v *= v; }
                     else if (op == DL_DENSE_SIGMOID_MUL) v = aux[m * ald] / (1.0f + expf(-v));
                     else if (op == DL_DENSE_SOFTCAP) v = prm * tanhf(v / prm);
+                    else if (op == DL_DENSE_SILU) v = v / (1.0f + expf(-v));
                     d0[m * ld] = v;
                 }
             }

@@ -29,19 +29,21 @@ __device__ __forceinline__ float conv_input(const DlMambaBatch& b, const float* 
     return conv_state[((size_t)b.seq_slot[n] * (taps - 1) + k) * channels + ch];
 }
 
-// out[row][ch] = silu(bias[ch] + sum_k w[ch][k] * input(pos - (taps-1) + k))
+// out[row][ch] = act(bias[ch] + sum_k w[ch][k] * input(pos - (taps-1) + k)) (+ input(pos) if residual)
 template <typename WT>
 __global__ void __launch_bounds__(256) mamba_conv_kernel(DlMambaBatch b, const float* __restrict__ in, long long ld, int in_off,
                                                          const WT* __restrict__ w, const WT* __restrict__ bias,
-                                                         const float* __restrict__ conv_state, float* __restrict__ out,
-                                                         int channels, int taps) {
+                                                         const float* __restrict__ conv_state, float* __restrict__ out, long long ld_out,
+                                                         int channels, int taps, int act, int residual) {
     const int m = blockIdx.x;
     const int n = b.row_seq[m], pos = b.pos[m];
     for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
-        float acc = ld_f(bias + ch);
+        float acc = bias ? ld_f(bias + ch) : 0.f;
         for (int k = 0; k < taps; ++k)
             acc = fmaf(ld_f(w + (size_t)ch * taps + k), conv_input(b, in, ld, in_off, conv_state, channels, taps, n, pos - (taps - 1) + k, ch), acc);
-        out[(size_t)m * channels + ch] = silu_f(acc);
+        if (act) acc = silu_f(acc);
+        if (residual) acc += in[(size_t)m * ld + in_off + ch];
+        out[(size_t)m * ld_out + ch] = acc;
     }
 }
 
@@ -61,22 +63,33 @@ __global__ void __launch_bounds__(256) mamba_conv_carry_kernel(DlMambaBatch b, c
     }
 }
 
+extern "C" int dl_causal_conv(const DlMambaBatch* batch, int M, int n_seq, const DlConvArgs* args, void* stream) {
+    const DlConvArgs& a = *args;
+    if (a.taps < 1 || a.taps > MB_MAX_TAPS) { dl_set_error("dl_causal_conv: 1..%d taps", MB_MAX_TAPS); return -1; }
+    if (a.out == a.in) { dl_set_error("dl_causal_conv: out must not alias in"); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    const int gy = (a.channels + 255) / 256;
+    if (a.wtype == DL_T_BF16)
+        mamba_conv_kernel<<<dim3(M, gy), 256, 0, st>>>(*batch, a.in, a.ld, a.in_off, (const __nv_bfloat16*)a.w, (const __nv_bfloat16*)a.bias, a.conv_state,
+                                                       a.out, a.ld_out, a.channels, a.taps, a.act, a.residual);
+    else
+        mamba_conv_kernel<<<dim3(M, gy), 256, 0, st>>>(*batch, a.in, a.ld, a.in_off, (const float*)a.w, (const float*)a.bias, a.conv_state,
+                                                       a.out, a.ld_out, a.channels, a.taps, a.act, a.residual);
+    LAYER_CHECK_LAUNCH("dl_causal_conv");
+    if (a.taps > 1) {
+        mamba_conv_carry_kernel<<<dim3(n_seq, gy), 256, 0, st>>>(*batch, a.in, a.ld, a.in_off, a.conv_state, a.channels, a.taps);
+        LAYER_CHECK_LAUNCH("dl_causal_conv carry");
+    }
+    return 0;
+}
+
 extern "C" int dl_mamba_conv(const DlMambaBatch* batch, int M, int n_seq, const float* in, long long ld, int in_off,
                              const void* w, const void* bias, int wtype, float* conv_state, float* out, int channels,
                              int taps, void* stream) {
-    if (taps < 1 || taps > MB_MAX_TAPS) { dl_set_error("dl_mamba_conv: 1..%d taps", MB_MAX_TAPS); return -1; }
-    cudaStream_t st = (cudaStream_t)stream;
-    const int gy = (channels + 255) / 256;
-    if (wtype == DL_T_BF16)
-        mamba_conv_kernel<<<dim3(M, gy), 256, 0, st>>>(*batch, in, ld, in_off, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, conv_state, out, channels, taps);
-    else
-        mamba_conv_kernel<<<dim3(M, gy), 256, 0, st>>>(*batch, in, ld, in_off, (const float*)w, (const float*)bias, conv_state, out, channels, taps);
-    LAYER_CHECK_LAUNCH("dl_mamba_conv");
-    if (taps > 1) {
-        mamba_conv_carry_kernel<<<dim3(n_seq, gy), 256, 0, st>>>(*batch, in, ld, in_off, conv_state, channels, taps);
-        LAYER_CHECK_LAUNCH("dl_mamba_conv carry");
-    }
-    return 0;
+    DlConvArgs a;
+    a.in = in; a.ld = ld; a.in_off = in_off; a.w = w; a.bias = bias; a.wtype = wtype; a.conv_state = conv_state;
+    a.out = out; a.ld_out = channels; a.channels = channels; a.taps = taps; a.act = 1; a.residual = 0;
+    return dl_causal_conv(batch, M, n_seq, &a, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

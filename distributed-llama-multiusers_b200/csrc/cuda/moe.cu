@@ -1,7 +1,9 @@
 // Routed experts: every token runs `top` of `experts` small feed-forward layers  W_down act(W_up h),  act = relu(.)^2,
-// and sums their outputs weighted by the router's scores.
+// and sums their outputs weighted by the router's scores.  Gated experts (a third matrix W_gate per expert) use
+// act = g * sigmoid(1.702 g) * (u + 1) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit) instead.
 //
-// Routing (dl_moe_select), from the router logits z[M][experts] (a dense product, f32):  s = sigmoid(z).  The experts
+// Routing (dl_moe_select), from the router logits z[M][experts] (a dense product, f32):  s = sigmoid(z), or s =
+// softmax(z) over all experts (`score` 1); the chosen weights may be multiplied by a constant (`scale`).  The experts
 // form `groups` equal groups of neighbours; a group's score is the sum of its `group_top` largest scores and only the
 // `keep` best groups stay eligible; the `top` eligible experts with the largest scores are chosen, their weights are
 // their scores (divided by the sum of the chosen scores if `renorm`).  Ties go to the lower index.  groups = keep = 1
@@ -45,7 +47,17 @@ __global__ void __launch_bounds__(MS_WARPS * 32) moe_select_kernel(DlMoeSelectAr
     float* s = sm + (size_t)warp * (2 * E + G);             // [E] scores, [E] working copy, [G] group scores (< 0: dropped)
     float* w = s + E;
     float* gs = w + E;
-    for (int e = lane; e < E; e += 32) w[e] = s[e] = sigmoid_f(a.z[(size_t)m * a.ldz + e]);
+    if (a.score == 1) {                                     // softmax over all experts
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, a.z[(size_t)m * a.ldz + e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(a.z[(size_t)m * a.ldz + e] - mx); s[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) w[e] = s[e] = s[e] / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) w[e] = s[e] = sigmoid_f(a.z[(size_t)m * a.ldz + e]);
+    }
     __syncwarp();
     if (G > 1) {
         for (int g = 0; g < G; ++g) {                        // the group's score: its group_top largest, picked off the copy
@@ -95,13 +107,19 @@ __global__ void __launch_bounds__(MS_WARPS * 32) moe_select_kernel(DlMoeSelectAr
         }
         __syncwarp();
     }
-    if (a.renorm && lane < a.top) a.wgt[(size_t)m * a.top + lane] /= total;
+    __syncwarp();
+    for (int k = lane; k < a.top; k += 32) {
+        float v = a.wgt[(size_t)m * a.top + k];
+        if (a.renorm) v /= total + 1e-20f;
+        if (a.scale != 0.f) v *= a.scale;
+        a.wgt[(size_t)m * a.top + k] = v;
+    }
 }
 
 extern "C" int dl_moe_select(const DlMoeSelectArgs* args, void* stream) {
     const DlMoeSelectArgs& a = *args;
     if (a.M < 1 || a.experts < 1 || a.groups < 1 || a.experts % a.groups || a.keep < 1 || a.keep > a.groups || a.top < 1 ||
-        a.top > a.keep * (a.experts / a.groups) || a.group_top < 1 || (a.renorm && a.top > 32)) {
+        a.top > a.keep * (a.experts / a.groups) || a.group_top < 1 || a.score < 0 || a.score > 1) {
         dl_set_error("dl_moe_select: %d experts in %d groups, keep %d, top %d", a.experts, a.groups, a.keep, a.top);
         return -1;
     }
@@ -162,7 +180,12 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_up_rows_kernel(DlMoeArgs a,
     const int m = pair / a.top, e = a.sel[pair];
     const WT* w = (const WT*)a.w_up + ((size_t)e * a.ff + f) * a.width;
     const float v = warp_dot<WT, RX>(w, a.x + (size_t)m * a.ldx, a.width, vec, lane);
-    if (lane == 0) {
+    if (a.w_gate != nullptr) {                // gated: g * sigmoid(1.702 g) * (u + 1) on the clamped products
+        const WT* wg = (const WT*)a.w_gate + ((size_t)e * a.ff + f) * a.width;
+        float g = warp_dot<WT, RX>(wg, a.x + (size_t)m * a.ldx, a.width, vec, lane), u = v;
+        if (a.limit > 0.f) { g = fminf(g, a.limit); u = fminf(fmaxf(u, -a.limit), a.limit); }
+        if (lane == 0) a.act[(size_t)pair * a.ff + f] = g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+    } else if (lane == 0) {
         const float r = fmaxf(v, 0.f);
         a.act[(size_t)pair * a.ff + f] = r * r;
     }
@@ -214,7 +237,8 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_down_rows_kernel(DlMoeArgs 
 
 template <typename WT, bool RX>
 static void launch_moe_rows(const DlMoeArgs& a, cudaStream_t st) {
-    const bool al = ((uintptr_t)a.w_up & 15) == 0 && ((uintptr_t)a.w_down & 15) == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.act & 15) == 0;
+    const bool al = ((uintptr_t)a.w_up & 15) == 0 && ((uintptr_t)a.w_gate & 15) == 0 && ((uintptr_t)a.w_down & 15) == 0 && ((uintptr_t)a.x & 15) == 0 &&
+                    ((uintptr_t)a.act & 15) == 0;
     const bool vec_up = al && a.width % 8 == 0 && a.ldx % 4 == 0, vec_down = al && a.ff % 8 == 0;
     moe_up_rows_kernel<WT, RX><<<dim3(a.M * a.top, (a.ff + MR_WARPS - 1) / MR_WARPS), MR_WARPS * 32, 0, st>>>(a, vec_up);
     moe_down_rows_kernel<WT, RX><<<dim3(a.M, (a.width + MR_WARPS - 1) / MR_WARPS), MR_WARPS * 32, 0, st>>>(a, vec_down);

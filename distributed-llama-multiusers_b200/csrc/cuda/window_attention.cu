@@ -11,6 +11,12 @@
 // Rotary: interleaved pairs (2i, 2i + 1), angle = pos * freqs[i] formed in f64, cos and sin multiplied by rope_scale
 // (frequency interpolation schemes that also scale the rotation's magnitude pass their factor here).
 //
+// The same kernels serve attention with values of their own (vdim > 0): the line is [ key[0 : dim] | value[0 : vdim] ],
+// written by attn_kv_write_kernel, which can divide every query and key head by its root mean square first.  Two more
+// options of the score side: a chunked mask (chunk > 0: j is visible to i only if floor(j / chunk) == floor(i / chunk),
+// chunks counted from position 0 of the sequence) and a sink per head (exp(sink_h) joins the softmax denominator,
+// with no key and no value).
+//
 // Kernels: the cache writer, which also turns the queries in place (one launch, cos and sin formed once per row and
 // pair); the per-row attention kernel (exact f32 arithmetic on either cache type; one CTA per
 // (row, key/value head), all query heads of the group share each staged page; pages outside the window are never
@@ -69,8 +75,51 @@ __global__ void __launch_bounds__(256) window_kv_write_kernel(DlWindowKvArgs a) 
     }
 }
 
+// Separate values, no rotary: one CTA per row, a warp per (query or key) head.  With qk_norm every head is divided by
+// sqrt(mean(head^2) + eps): the queries in place, the keys on their way into the cache.  The values are copied behind
+// the keys.
+template <typename CT>
+__global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
+    const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int pos = a.pos[m], slot = a.slot[m];
+    const int page = a.block_table[(size_t)slot * a.max_pages + pos / WA_PAGE];
+    const int LD = a.dim + a.vdim;
+    CT* line0 = (CT*)a.cache + (((size_t)page * a.kv_heads) * WA_PAGE + pos % WA_PAGE) * LD;
+    const size_t head_step = (size_t)WA_PAGE * LD;
+    const int nq = a.q ? a.q_heads : 0;
+    for (int h = warp; h < a.kv_heads + nq; h += nw) {
+        const bool is_k = h < a.kv_heads;
+        float* qh = is_k ? nullptr : a.q + (size_t)m * a.ldq + (size_t)(h - a.kv_heads) * a.dim;
+        const float* src = is_k ? a.k + (size_t)m * a.ld + (size_t)h * a.dim : qh;
+        float inv = 1.f;
+        if (a.qk_norm) {
+            float ss = 0.f;
+            for (int i = lane; i < a.dim; i += 32) ss = fmaf(src[i], src[i], ss);
+            inv = 1.f / sqrtf(warp_sum(ss) / (float)a.dim + a.eps);
+        }
+        if (is_k) {
+            CT* dst = line0 + h * head_step;
+            for (int i = lane; i < a.dim; i += 32) st_f(dst + i, src[i] * inv);
+        } else if (a.qk_norm) {
+            for (int i = lane; i < a.dim; i += 32) qh[i] = src[i] * inv;
+        }
+    }
+    for (int t = threadIdx.x; t < a.kv_heads * a.vdim; t += blockDim.x) {
+        const int g = t / a.vdim, i = t - g * a.vdim;
+        st_f(line0 + g * head_step + a.dim + i, a.v[(size_t)m * a.ldv + t]);
+    }
+}
+
 extern "C" int dl_window_kv_write(const DlWindowKvArgs* args, int M, void* stream) {
     const DlWindowKvArgs& a = *args;
+    if (a.v != nullptr) {
+        if (a.rope_dims != 0 || a.vdim < 1 || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: separate values come without rotary (rope_dims %d, vdim %d)", a.rope_dims, a.vdim); return -1; }
+        if (a.ctype == DL_T_BF16) attn_kv_write_kernel<__nv_bfloat16><<<M, 256, 0, (cudaStream_t)stream>>>(a);
+        else attn_kv_write_kernel<float><<<M, 256, 0, (cudaStream_t)stream>>>(a);
+        LAYER_CHECK_LAUNCH("dl_window_kv_write");
+        return 0;
+    }
+    if (a.qk_norm) { dl_set_error("dl_window_kv_write: qk_norm belongs to the separate-value form"); return -1; }
     if (a.rope_dims > a.dim || (a.rope_dims & 1) || a.rope_dims > 2 * WK_MAX_PAIRS || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: bad rotary or page size"); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     if (a.ctype == DL_T_BF16) window_kv_write_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(a);
@@ -86,19 +135,19 @@ template <typename CT>
 __global__ void window_attention_kernel(DlWindowAttnArgs a) {
     extern __shared__ float sm[];
     const int m = blockIdx.x, g = blockIdx.y;
-    const int rep = a.heads / a.kv_heads, D = a.dim, RD = a.rope_dims, LD = D + RD, LP = LD + 1;
+    const int rep = a.heads / a.kv_heads, D = a.dim, RD = a.rope_dims, DV = a.vdim > 0 ? a.vdim : D;
+    const int LD = D + (a.vdim > 0 ? a.vdim : RD), LP = LD + 1;
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* q_s = sm;                                   // [rep][D]
     float* tile = q_s + (size_t)rep * D;               // [WA_PAGE][LD + 1]
-    float* acc = tile + (size_t)WA_PAGE * LP;          // [rep][D]
-    float* p_s = acc + (size_t)rep * D;                // [nw][WA_PAGE]
+    float* acc = tile + (size_t)WA_PAGE * LP;          // [rep][DV]
+    float* p_s = acc + (size_t)rep * DV;               // [nw][WA_PAGE]
     float* ml = p_s + (size_t)nw * WA_PAGE;            // [rep][2]
     const int pos = a.pos[m], slot = a.slot[m];
-    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;      // oldest visible position
-    for (int t = threadIdx.x; t < rep * D; t += blockDim.x) {
-        q_s[t] = a.q[(size_t)m * a.ldq + (size_t)g * rep * D + t];
-        acc[t] = 0.f;
-    }
+    int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;            // oldest visible position
+    if (a.chunk > 0) first = max(first, pos / a.chunk * a.chunk);
+    for (int t = threadIdx.x; t < rep * D; t += blockDim.x) q_s[t] = a.q[(size_t)m * a.ldq + (size_t)g * rep * D + t];
+    for (int t = threadIdx.x; t < rep * DV; t += blockDim.x) acc[t] = 0.f;
     for (int t = threadIdx.x; t < rep; t += blockDim.x) { ml[2 * t] = -INFINITY; ml[2 * t + 1] = 0.f; }
     for (int pg = first / WA_PAGE; pg <= pos / WA_PAGE; ++pg) {
         __syncthreads();
@@ -126,10 +175,10 @@ __global__ void window_attention_kernel(DlWindowAttnArgs a) {
             p_s[warp * WA_PAGE + lane] = p;
             __syncwarp();
             if (lane == 0) { ml[2 * h] = m_new; ml[2 * h + 1] = l_new; }
-            float* ah = acc + (size_t)h * D;
+            float* ah = acc + (size_t)h * DV;
             const float* ps = p_s + warp * WA_PAGE;
-            for (int d = lane; d < D; d += 32) {
-                const int col = d < RD ? D + d : d;              // the value's first entries sit behind the key
+            for (int d = lane; d < DV; d += 32) {
+                const int col = (a.vdim > 0 || d < RD) ? D + d : d;      // own values, or the value's first entries, sit behind the key
                 float v = ah[d] * alpha;
                 for (int j = j_lo; j < j_hi; ++j) v = fmaf(ps[j], tile[j * LP + col], v);
                 ah[d] = v;
@@ -138,12 +187,17 @@ __global__ void window_attention_kernel(DlWindowAttnArgs a) {
         }
     }
     __syncthreads();
-    for (int t = threadIdx.x; t < rep * D; t += blockDim.x)
-        a.out[(size_t)m * a.ldo + (size_t)g * rep * D + t] = acc[t] / ml[2 * (t / D) + 1];
+    for (int t = threadIdx.x; t < rep * DV; t += blockDim.x) {
+        const int h = t / DV;
+        float l = ml[2 * h + 1];
+        if (a.sink) l += expf(a.sink[g * rep + h] - ml[2 * h]);
+        a.out[(size_t)m * a.ldo + (size_t)g * rep * DV + t] = acc[t] / l;
+    }
 }
 
 static int window_args_ok(const DlWindowAttnArgs& a, const char* who) {
-    if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.rope_dims > a.dim || a.window < 0 || a.page_size != WA_PAGE) {
+    if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.rope_dims > a.dim || a.window < 0 || a.page_size != WA_PAGE ||
+        a.vdim < 0 || a.chunk < 0 || (a.vdim > 0 && a.rope_dims != 0)) {
         dl_set_error("%s: bad shape (heads %d / %d, dim %d, rotary %d, window %d, page %d)", who, a.heads, a.kv_heads, a.dim, a.rope_dims, a.window, a.page_size);
         return -1;
     }
@@ -153,8 +207,8 @@ static int window_args_ok(const DlWindowAttnArgs& a, const char* who) {
 extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* stream) {
     const DlWindowAttnArgs& a = *args;
     if (window_args_ok(a, "dl_window_attention")) return -1;
-    const int rep = a.heads / a.kv_heads, nw = rep < 8 ? rep : 8, LD = a.dim + a.rope_dims;
-    const size_t smem = ((size_t)2 * rep * a.dim + (size_t)WA_PAGE * (LD + 1) + (size_t)nw * WA_PAGE + 2 * (size_t)rep) * sizeof(float);
+    const int rep = a.heads / a.kv_heads, nw = rep < 8 ? rep : 8, LD = a.dim + (a.vdim > 0 ? a.vdim : a.rope_dims), DV = a.vdim > 0 ? a.vdim : a.dim;
+    const size_t smem = ((size_t)rep * (a.dim + DV) + (size_t)WA_PAGE * (LD + 1) + (size_t)nw * WA_PAGE + 2 * (size_t)rep) * sizeof(float);
     if (smem > 227 * 1024) { dl_set_error("dl_window_attention: %d heads per group x dim %d need %zu bytes of shared memory", rep, a.dim, smem); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(M, a.kv_heads);
@@ -215,7 +269,8 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
     constexpr int D = 16 * DK, NV = D / 8;
     extern __shared__ __align__(16) uint8_t smraw[];
     __shared__ int s_row[WM_ROWS];
-    const int RD = a.rope_dims, LD = D + RD, LDS = wm_line_stride(LD);
+    const int RD = a.rope_dims, LD = D + (a.vdim > 0 ? a.vdim : RD), LDS = wm_line_stride(LD);
+    const bool own_v = a.vdim > 0;                                                  // values behind the key (vdim == dim here)
     constexpr int QS = D + 8;                                                       // row stride of the query tile (bf16)
     __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][WA_PAGE][LDS]
     __nv_bfloat16* q_s = kv_s + (size_t)2 * WA_PAGE * LDS;                          // [WM_ROWS][QS]: the stacked queries
@@ -227,7 +282,8 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
     while (n_rows < rq && s_row[n_rows] >= 0) ++n_rows;
     if (n_rows == 0) return;
     const int p_first = a.pos[s_row[0]], p_last = p_first + n_rows - 1, slot = a.slot[s_row[0]];
-    const int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    if (a.chunk > 0) lo = max(lo, p_first / a.chunk * a.chunk);
     int pg_lo = lo / WA_PAGE, pg_hi = p_last / WA_PAGE;
     if (n_splits > 1) {                  // this CTA's share of the tile's pages (possibly none)
         const int per = (pg_hi - pg_lo + n_splits) / n_splits;
@@ -244,6 +300,8 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
     const int r0 = s0 / rep, r1 = s1 / rep;
     const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
     const int pos0 = p_first + r0, pos1 = p_first + r1;
+    const int cs0 = a.chunk > 0 ? pos0 / a.chunk * a.chunk : 0, cs1 = a.chunk > 0 ? pos1 / a.chunk * a.chunk : 0;      // first position of the row's chunk
+    const int cs_last = a.chunk > 0 ? p_last / a.chunk * a.chunk : 0;
     // the tile's queries, rounded to bf16, into shared memory (A fragments come from there by ldmatrix: registers are
     // what limits the CTAs per SM)
     for (int idx = threadIdx.x; idx < WM_ROWS * (D / 4); idx += 128) {
@@ -297,7 +355,7 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
         }
         // scale and soft cap (base-2 scores), window mask (skipped on pages that every row of the tile sees whole)
         const int pg_first = pg * WA_PAGE;
-        const bool whole = pg_first + WA_PAGE - 1 <= p_first && (a.window == 0 || p_last - pg_first < a.window);      // stacked rows without a position are never stored
+        const bool whole = pg_first + WA_PAGE - 1 <= p_first && (a.window == 0 || p_last - pg_first < a.window) && pg_first >= cs_last;      // stacked rows without a position are never stored
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
@@ -308,7 +366,7 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
                 if (!whole) {
                     const int j = pg_first + n * 8 + tig * 2 + (e & 1);
                     const int pr = (e < 2) ? pos0 : pos1;
-                    const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window);
+                    const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window) && j >= ((e < 2) ? cs0 : cs1);
                     s2 = vis ? s2 : -INFINITY;
                 }
                 sc[n][e] = s2;
@@ -343,7 +401,7 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
 #pragma unroll
             for (int vp = 0; vp < NV / 2; ++vp) {
                 const int vt = 2 * vp + (mat >> 1);
-                const int col = vt * 8 < RD ? D + vt * 8 : vt * 8;            // the value's first entries sit behind the key
+                const int col = (own_v || vt * 8 < RD) ? D + vt * 8 : vt * 8;      // own values, or the value's first entries, sit behind the key
                 uint32_t b[4];
                 ldmatrix_x4_trans(b, kv + (size_t)(ks * 16 + (mat & 1) * 8 + rr) * LDS + col);
                 mma_bf16(o[2 * vp], pa, b[0], b[1]);
@@ -369,6 +427,10 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
             if (tig == 0) { dst[D] = m1 * WM_LN2; dst[D + 1] = l1; }
         }
         return;
+    }
+    if (a.sink) {                        // the sink's share of the denominator, in the base-2 scale of the running maximum
+        if (ok0) l0 += fast_ex2(a.sink[g * rep + s0 % rep] * WM_LOG2E - m0);
+        if (ok1) l1 += fast_ex2(a.sink[g * rep + s1 % rep] * WM_LOG2E - m1);
     }
     if (ok0) {
         float* dst = a.out + (size_t)s_row[r0] * a.ldo + (size_t)(g * rep + s0 % rep) * D;
@@ -411,6 +473,7 @@ __global__ void __launch_bounds__(128) window_merge_kernel(DlWindowAttnArgs a, c
             l += l_s[hg * n_splits + k] * e;
             w_s[hg * n_splits + k] = e;
         }
+        if (a.sink) l += expf(a.sink[g * rep + hg] - mx);
         const float inv = 1.f / l;
         for (int k = 0; k < n_splits; ++k) w_s[hg * n_splits + k] *= inv;
     }
@@ -450,6 +513,7 @@ extern "C" int dl_window_attention_tc(const DlWindowAttnArgs* args, const int* t
                                       float* partial, void* stream) {
     const DlWindowAttnArgs& a = *args;
     if (window_args_ok(a, "dl_window_attention_tc")) return -1;
+    if (a.vdim > 0 && a.vdim != a.dim) { dl_set_error("dl_window_attention_tc: values of their own must be as wide as the keys (dim %d, vdim %d)", a.dim, a.vdim); return -1; }
     if (dl_window_attention_tc_supported(a.heads, a.kv_heads, a.dim, a.rope_dims, a.ctype) != 0 || rq < 1 || rq > dl_window_tc_rows(a.heads, a.kv_heads) ||
         (a.ldq & 3) || (a.ldo & 1) || ((uintptr_t)a.q & 15)) {
         dl_set_error("dl_window_attention_tc: sizes not supported (heads %d / %d, dim %d, rotary %d, rq %d)", a.heads, a.kv_heads, a.dim, a.rope_dims, rq);
@@ -457,7 +521,7 @@ extern "C" int dl_window_attention_tc(const DlWindowAttnArgs* args, const int* t
     }
     if (n_tiles < 1) return 0;
     if (n_splits < 1 || n_splits > WM_MAX_SPLITS || (n_splits > 1 && partial == nullptr)) { dl_set_error("dl_window_attention_tc: n_splits %d without scratch", n_splits); return -1; }
-    const size_t smem = ((size_t)2 * WA_PAGE * wm_line_stride(a.dim + a.rope_dims) + (size_t)WM_ROWS * (a.dim + 8)) * sizeof(__nv_bfloat16);
+    const size_t smem = ((size_t)2 * WA_PAGE * wm_line_stride(a.dim + (a.vdim > 0 ? a.vdim : a.rope_dims)) + (size_t)WM_ROWS * (a.dim + 8)) * sizeof(__nv_bfloat16);
     dim3 grid(n_tiles, a.kv_heads, n_splits);
     cudaStream_t st = (cudaStream_t)stream;
     switch (a.dim / 16) {

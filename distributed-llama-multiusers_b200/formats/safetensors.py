@@ -68,7 +68,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]):
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise ValueError(f"tensor {name}: unsupported dtype {t.dtype}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""      # reshape: a tensor without dimensions too
         meta[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

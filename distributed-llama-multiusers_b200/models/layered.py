@@ -4,7 +4,13 @@ meets the residual stream is the architecture's ``residual`` style (``RESIDUAL_S
 
     "sandwich":  x <- x + post_norm(sub(pre_norm(x)))                    norm weights stored around zero (Ribivik)
     "hyper":     u = sum_s in[s] x_s;  y = sub(norm(u));  x_t <- sum_s mix[s][t] x_s + m out[t] y      (Sunesun)
-                 `streams` copies of the stream (hyper-connections); without them the plain x <- x + m sub(norm(x))
+                 `streams` copies of the stream (hyper-connections); without them the plain x <- x + m sub(norm(x)),
+                 which is how Venadra's pre-norm layers run (one stream, m = 1)
+
+What a design fixes without saying it in config.json (how its attention masks, whether its experts are gated, ...) is
+its entry of ``DESIGNS``; everything config.json gives is read from there.  A configuration with ``canon: {taps}`` puts a
+short causal convolution in front of every mixer: h <- h + conv(h) on the normed input, the last taps - 1 inputs kept per
+sequence slot and layer.
 
 The mixers and feed-forwards are looked up by name (``MIXERS`` / ``FEED_FORWARDS`` below), so another design composes
 the same mechanisms with its own sizes and order; ``ARCHITECTURES`` in models/registry.py maps an architecture name to
@@ -13,12 +19,16 @@ this engine.  Mixers here:
 * ``latent_attention`` -- attention whose keys and values are up-projections of one small cached latent per token plus
   a rotated key part shared by all heads; a layer may read the cache another layer writes (``kv_from``);
 * ``mamba2`` -- a gated selective state-space recurrence with a short causal convolution in front;
-* ``attention`` -- grouped-query attention over a sliding window whose values are its keys (one projection, one cache
-  line per token and key/value head), interleaved rotary positions with optional frequency interpolation, soft-capped
-  scores.
+* ``attention`` -- grouped-query attention over a paged cache of one line per token and key/value head.  Per design:
+  values that are the keys (one projection) or have a projection of their own; a sliding window or a chunked mask;
+  interleaved rotary positions with optional frequency interpolation, or none; soft-capped scores; queries and keys
+  divided by their root mean square; a sink per head in the softmax denominator; a sigmoid output gate;
+* ``lightning`` -- linear attention with a fixed decay per head and an f32 state [dim][vdim] per head and slot, SiLU on
+  q, k and v, an RMS norm over the concatenated heads and a sigmoid output gate.
 
-Feed-forwards: ``dense`` and ``moe`` (sigmoid-scored, group-limited routing over small squared-ReLU experts).  A layer
-with ``weights_of: j`` runs layer j's weights on a cache or state of its own (a looped layer).
+Feed-forwards: ``dense`` (squared ReLU, or PolyNorm) and ``moe`` (sigmoid-scored, group-limited routing over small
+squared-ReLU experts; or softmax-scored, renormalised routing over gated experts).  A layer with ``weights_of: j`` runs
+layer j's weights on a cache or state of its own (a looped layer).
 
 What the engine shares with ``LlamaEngine`` is the serving surface (slots, rows with per-row positions, paged token
 cache from ``PageAllocator``, ``forward`` / ``decode_step_greedy`` / ``prefill``), so the scheduler, the batching loop
@@ -55,8 +65,19 @@ class LayerSpec:
     weights_of: Optional[int] = None       # run that layer's weights (norms, mixer, feed-forward) on a cache / state of its own
 
 
-# how sublayers meet the residual stream, by architecture name
-RESIDUAL_STYLES = {"Ribivik": "sandwich", "Sunesun": "hyper"}
+# What a design fixes outside its config.json, by architecture name.  residual: how sublayers meet the residual stream.
+# attention: values ("keys": the keys as projected | "own": a projection v), mask (what mask.size means: "window" |
+# "chunk"), qk_norm, sink (tensor `sink` [heads]), gate (tensor `g`: sigmoid output gate).  dense_act: "relu2" |
+# "polynorm" (tensor `act` [4]).  moe: score ("sigmoid" | "softmax"), renorm, gated (tensors e<n>.gate; expert.limit).
+DESIGNS = {
+    "Ribivik": {"residual": "sandwich"},
+    "Sunesun": {"residual": "hyper"},
+    "Venadra": {"residual": "hyper",
+                "attention": {"values": "own", "mask": "chunk", "qk_norm": True, "sink": True, "gate": True},
+                "dense_act": "polynorm",
+                "moe": {"score": "softmax", "renorm": True, "gated": True}},
+}
+RESIDUAL_STYLES = {name: d["residual"] for name, d in DESIGNS.items()}
 
 
 @dataclass
@@ -73,6 +94,8 @@ class LayerListConfig:
     residual_mult: float = 1.0             # "hyper": every sublayer output is multiplied by it on its way into the stream
     streams: int = 1                       # "hyper": copies of the residual stream
     hyper_weights: bool = False            # the layers bring hc<q>.in / .out / .mix tensors (else the plain sum)
+    canon_taps: int = 0                    # > 0: h <- h + conv(h) over the last `taps` normed inputs, in front of every mixer
+    traits: dict = field(default_factory=dict)      # the design's entry of DESIGNS
 
     # the serving code reads these names from every engine's header
     @property
@@ -96,7 +119,8 @@ class LayerListConfig:
                                layers=layers, residual=RESIDUAL_STYLES.get(arch, "sandwich"),
                                embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)),
                                residual_mult=float(c.get("residual_mult", 1.0)),
-                               streams=int(c.get("streams") or 1), hyper_weights=bool(c.get("streams")))
+                               streams=int(c.get("streams") or 1), hyper_weights=bool(c.get("streams")),
+                               canon_taps=int((c.get("canon") or {}).get("taps") or 0), traits=DESIGNS.get(arch, {}))
 
     @staticmethod
     def load(model_dir: str) -> "LayerListConfig":
@@ -153,6 +177,7 @@ class DenseWeight:
 
 TC_MIN_ROWS = int(os.environ.get("DLLAMA_LAYERS_TC_MIN_ROWS", "32"))
 CHUNKED_SCAN_MIN_ROWS = 256  # a batch holding this many rows of one sequence runs the recurrence chunk-parallel
+LIGHTNING_CHUNKED_MIN_ROWS = 128     # the same for linear attention (chunks of 64 rows)
 TC_HEADS_MIN_ROWS = 256      # per-head products (one small GEMM per head) take the tensor-core path from this many rows
 GRAPH_MAX_ROWS = 64          # batches up to this many rows are replayed from CUDA graphs
 WINDOW_MAX_SPLITS = 32       # most CTAs that share one tile's pages in the windowed-attention kernel
@@ -276,12 +301,16 @@ class Mamba2Mixer:
 
 
 class DenseFeedForward:
-    """Tensors <prefix>up, down:  W_down relu(W_up h)^2."""
+    """Tensors <prefix>up, down:  W_down act(W_up h).  act = relu(.)^2, or (design trait dense_act "polynorm", tensor
+    <prefix>act = [a, b, c, e]) PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e with N the RMS normalisation of a row."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng = eng
         self.ff = int(m["ff"])
         self.w_up, self.w_down = eng.dense_weight(eng.weight(prefix + "up")), eng.dense_weight(eng.weight(prefix + "down"))
+        self.poly = eng.vector(prefix + "act") if eng.cfg.traits.get("dense_act") == "polynorm" else None
+        if self.poly is not None and tuple(self.poly.shape) != (4,):
+            raise ValueError(f"layer {index}: {prefix}act has shape {tuple(self.poly.shape)}")
 
     def scratch(self) -> Dict[str, int]:
         return {"up": self.ff}
@@ -291,94 +320,196 @@ class DenseFeedForward:
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
         e, L = self.eng, self.eng.L
-        up = e.buf("up")
-        e.mm(self.w_up, h, up, M, epi=L.DENSE_RELU2, src="h")
+        up = e.buf("up", self.ff)
+        if self.poly is not None:
+            e.mm(self.w_up, h, up, M, src="h")
+            L.poly_norm(up, up, M, self.ff, self.poly, e.cfg.norm_eps)
+        else:
+            e.mm(self.w_up, h, up, M, epi=L.DENSE_RELU2, src="h")
         e.mm(self.w_down, up, y, M)
 
 
 class WindowAttentionMixer:
-    """Tensors <prefix>q, k, o.  Sizes: heads, kv_heads, dim (per-head query / key size), vdim (= dim: the values are the
-    keys as projected, there is no value projection), scale, softcap (0 / absent: none), mask.size (the window: a
-    position sees itself and the size - 1 before it; absent: everything before it), rot {base, dims, scaling}.
-    The cache holds one line per token and key/value head: the rotated key followed by the unrotated head of k."""
+    """Grouped-query attention over a paged cache.  Sizes: heads, kv_heads, dim (per-head query / key size), vdim, scale,
+    softcap (0 / absent: none), mask.size, rot {base, dims, scaling} (absent: positions do not enter the scores).
+    The design's `attention` traits choose the rest:
+      values "keys" (default): tensors <prefix>q, k, o; the values are the keys as projected (vdim = dim), the cache line
+             holds the rotated key followed by the unrotated head of k;
+      values "own": a projection <prefix>v of vdim numbers per key/value head, the line holds key + value (no rotary);
+      mask "window" (default): a position sees itself and the mask.size - 1 before it (absent: everything before it);
+      mask "chunk": position i sees j <= i with floor(j / size) = floor(i / size), chunks counted from position 0;
+      qk_norm: every query and key head is divided by its root mean square (eps of the model) before the scores;
+      sink: <prefix>sink [heads], exp(sink_h) joins the softmax denominator without a key or a value;
+      gate: <prefix>g, the concatenated heads are multiplied by sigmoid(W_g h) before the output projection."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str, share: Optional["WindowAttentionMixer"] = None):
         self.eng, self.index = eng, index
+        tr = eng.cfg.traits.get("attention") or {}
+        self.own_v, self.qk_norm = tr.get("values", "keys") == "own", bool(tr.get("qk_norm"))
         self.H, self.G, self.dim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
-        if int(m.get("vdim", self.dim)) != self.dim:
+        self.vdim = int(m.get("vdim", self.dim))
+        if not self.own_v and self.vdim != self.dim:
             raise ValueError(f"layer {index}: the values are the keys, so vdim must equal dim")
         if self.H % self.G:
             raise ValueError(f"layer {index}: {self.H} heads do not divide into {self.G} key/value heads")
         self.scale, self.softcap = float(m["scale"]), float(m.get("softcap") or 0.0)
-        self.window = int((m.get("mask") or {}).get("size") or 0)
+        size = int((m.get("mask") or {}).get("size") or 0)
+        self.window, self.chunk = (0, size) if tr.get("mask", "window") == "chunk" else (size, 0)
         rot = m.get("rot") or {"base": 10000.0, "dims": 0}
         self.rope_dims = int(rot["dims"])
-        if self.rope_dims > self.dim or self.rope_dims % 2:
+        if self.rope_dims > self.dim or self.rope_dims % 2 or (self.own_v and self.rope_dims):
             raise ValueError(f"layer {index}: rotary dims {self.rope_dims} do not fit dim {self.dim}")
         freqs, self.rope_mag = interpolated_rotary(float(rot["base"]), self.rope_dims, rot.get("scaling"))
         self.freqs = freqs.to(eng.device) if self.rope_dims else torch.zeros(1, dtype=torch.float64, device=eng.device)
+        H, G, d, dv = self.H, self.G, self.dim, self.vdim
         if share is None:
             W, D = eng.weight, eng.dense_weight
             wq, wk = W(prefix + "q"), W(prefix + "k")
-            if tuple(wq.shape) != (self.H * self.dim, eng.cfg.width) or tuple(wk.shape) != (self.G * self.dim, eng.cfg.width):
+            if tuple(wq.shape) != (H * d, eng.cfg.width) or tuple(wk.shape) != (G * d, eng.cfg.width):
                 raise ValueError(f"layer {index}: q / k have shapes {tuple(wq.shape)} / {tuple(wk.shape)}")
-            self.w_qk = D(torch.cat([wq, wk], 0).contiguous())         # one product for queries and keys
+            parts = [wq, wk]
+            if self.own_v:
+                wv = W(prefix + "v")
+                if tuple(wv.shape) != (G * dv, eng.cfg.width):
+                    raise ValueError(f"layer {index}: v has shape {tuple(wv.shape)}")
+                parts.append(wv)
+            self.w_qk = D(torch.cat(parts, 0).contiguous())            # one product for queries, keys (and values)
             self.w_o = D(W(prefix + "o"))
+            self.w_g = D(W(prefix + "g")) if tr.get("gate") else None
+            self.sink = eng.vector(prefix + "sink") if tr.get("sink") else None
+            if self.sink is not None and tuple(self.sink.shape) != (H,):
+                raise ValueError(f"layer {index}: sink has shape {tuple(self.sink.shape)}")
         else:
-            self.w_qk, self.w_o = share.w_qk, share.w_o
+            self.w_qk, self.w_o, self.w_g, self.sink = share.w_qk, share.w_o, share.w_g, share.sink
         self.owns_weights = share is None
-        self.line = self.dim + self.rope_dims
-        self.cache = torch.zeros(eng.n_pages, self.G, PAGE, self.line, dtype=eng.wdtype, device=eng.device)
+        self.line = d + (dv if self.own_v else self.rope_dims)
+        self.cache = torch.zeros(eng.n_pages, G, PAGE, self.line, dtype=eng.wdtype, device=eng.device)
         # bf16 caches of sizes the tensor-core kernel takes: tiles of tc_rq consecutive rows of a sequence (0: per-row kernel)
         L = eng.L
         self.tc_rq = 0
-        if eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0" and \
-                L.window_tc_supported(self.H, self.G, self.dim, self.rope_dims, eng.wdtype):
-            self.tc_rq = L.window_tc_rows(self.H, self.G)
+        if eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0" and dv == d and \
+                L.window_tc_supported(H, G, d, self.rope_dims, eng.wdtype):
+            self.tc_rq = L.window_tc_rows(H, G)
 
     def scratch(self) -> Dict[str, int]:
-        return {"qk": (self.H + self.G) * self.dim, "o": self.H * self.dim}
+        n = {"qk": (self.H + self.G) * self.dim + (self.G * self.vdim if self.own_v else 0), "o": self.H * self.vdim}
+        if self.w_g is not None:
+            n["og"] = self.H * self.vdim
+        return n
 
     def bind(self, mixers: list):
         pass
 
     def weight_bytes(self) -> int:
-        return self.w_qk.nbytes() + self.w_o.nbytes() if self.owns_weights else 0
+        if not self.owns_weights:
+            return 0
+        return self.w_qk.nbytes() + self.w_o.nbytes() + (self.w_g.nbytes() if self.w_g is not None else 0)
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
         e, L = self.eng, self.eng.L
-        H, G, d, rd = self.H, self.G, self.dim, self.rope_dims
-        qk, o = e.buf("qk", (H + G) * d), e.buf("o", H * d)
+        H, G, d, dv, rd = self.H, self.G, self.dim, self.vdim, self.rope_dims
+        nqk = (H + G) * d
+        qk, o = e.buf("qk", nqk + (G * dv if self.own_v else 0)), e.buf("o", H * dv)
         e.mm(self.w_qk, h, qk, M, src="h")
-        # one launch: the keys go into the cache (rotated key + unrotated head) and the queries are rotated in place
-        L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache,
-                          q=qk, q_heads=H)
+        # one launch: the keys (and values) go into the cache and the queries are rotated / normalised in place
+        if self.own_v:
+            L.window_kv_write(qk[:, H * d:], M, G, d, 0, self.freqs, 1.0, e.pos, e.slot, e.block_table, self.cache, q=qk, q_heads=H,
+                              v=qk[:, nqk:], vdim=dv, qk_norm=self.qk_norm, eps=e.cfg.norm_eps)
+        else:
+            L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache,
+                              q=qk, q_heads=H)
+        opts = dict(vdim=dv if self.own_v else 0, chunk=self.chunk, sink=self.sink)
         if self.tc_rq:
             tile_rows, n_tiles = e.window_tiles(self.tc_rq)
             # few tiles (decoding): several CTAs share a tile's pages.  The share count depends on the tiling only (not on
             # the positions), so a captured graph stays valid as the sequences grow
-            pages = (self.window + PAGE - 1) // PAGE + 1 if self.window else e.max_pages
+            span = self.window or self.chunk
+            pages = (span + PAGE - 1) // PAGE + 1 if span else e.max_pages
             n_splits = 1
             if n_tiles * G <= 2 * e.n_sms:
                 n_splits = max(1, min(pages, WINDOW_MAX_SPLITS, (WINDOW_CTAS_PER_SM * e.n_sms) // (n_tiles * G)))
             L.window_attention_tc(qk, o, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
-                                  self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, e.window_partial(d) if n_splits > 1 else None)
+                                  self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, e.window_partial(d) if n_splits > 1 else None,
+                                  **opts)
         else:
             L.window_attention(qk, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
-                               self.cache)
+                               self.cache, **opts)
+        if self.w_g is not None:
+            og = e.buf("og", H * dv)
+            e.mm(self.w_g, h, og, M, epi=L.DENSE_SIGMOID_MUL, aux=o, src="h")
+            o = og
         e.mm(self.w_o, o, y, M)
 
 
+class LightningMixer:
+    """Linear attention with a fixed decay per head.  Tensors <prefix>q, k, v, g, o, norm.  Sizes: heads, dim, vdim,
+    decay [heads].  q = silu(W_q h), k = silu(W_k h), v = silu(W_v h); per head S <- decay_h S + k v^T (f32, one state
+    [dim][vdim] per slot and head), o = S^T q; the concatenated heads are RMS-normed together (weight `norm`), multiplied
+    by sigmoid(W_g h) and projected by W_o."""
+
+    def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str, share: Optional["LightningMixer"] = None):
+        self.eng, self.index = eng, index
+        self.H, self.dim, self.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+        decay = [float(x) for x in m["decay"]]
+        if len(decay) != self.H or not all(0.0 <= x <= 1.0 for x in decay):
+            raise ValueError(f"layer {index}: decay must give one number in [0, 1] per head")
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=eng.device)
+        H, d, dv = self.H, self.dim, self.vdim
+        if share is None:
+            W, D = eng.weight, eng.dense_weight
+            wq, wk, wv = W(prefix + "q"), W(prefix + "k"), W(prefix + "v")
+            if tuple(wq.shape) != (H * d, eng.cfg.width) or tuple(wk.shape) != (H * d, eng.cfg.width) or tuple(wv.shape) != (H * dv, eng.cfg.width):
+                raise ValueError(f"layer {index}: q / k / v have shapes {tuple(wq.shape)} / {tuple(wk.shape)} / {tuple(wv.shape)}")
+            self.w_qkv = D(torch.cat([wq, wk, wv], 0).contiguous())    # one product, SiLU in its epilogue
+            self.w_g, self.w_o, self.norm = D(W(prefix + "g")), D(W(prefix + "o")), eng.vector(prefix + "norm")
+            if tuple(self.norm.shape) != (H * dv,):
+                raise ValueError(f"layer {index}: norm has shape {tuple(self.norm.shape)}")
+        else:
+            self.w_qkv, self.w_g, self.w_o, self.norm = share.w_qkv, share.w_g, share.w_o, share.norm
+        self.owns_weights = share is None
+        self.state = torch.zeros(eng.n_slots, H, d, dv, dtype=torch.float32, device=eng.device)
+        self.chunked = eng.L.lightning_chunked_supported(d, dv)
+
+    def scratch(self) -> Dict[str, int]:
+        return {"lqkv": self.H * (2 * self.dim + self.vdim), "ys": self.H * self.vdim, "yn": self.H * self.vdim, "og": self.H * self.vdim}
+
+    def bind(self, mixers: list):
+        pass
+
+    def weight_bytes(self) -> int:
+        return self.w_qkv.nbytes() + self.w_g.nbytes() + self.w_o.nbytes() if self.owns_weights else 0
+
+    def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
+        e, L = self.eng, self.eng.L
+        H, d, dv = self.H, self.dim, self.vdim
+        qkv, ys, yn, og = e.buf("lqkv", H * (2 * d + dv)), e.buf("ys", H * dv), e.buf("yn", H * dv), e.buf("og", H * dv)
+        e.mm(self.w_qkv, h, qkv, M, epi=L.DENSE_SILU, src="h")
+        chunks = e.lightning_chunks if self.chunked else 0
+        L.lightning_scan(e.mamba_batch, e.n_seq, qkv, qkv[:, H * d:], qkv[:, 2 * H * d:], self.decay, ys, self.state, H, d, dv,
+                         max_chunks=chunks, scratch=e.lightning_scratch(self) if chunks else None)
+        L.rms_norm(ys, yn, M, H * dv, e.cfg.norm_eps, w=self.norm)
+        e.mm(self.w_g, h, og, M, epi=L.DENSE_SIGMOID_MUL, aux=yn, src="h")
+        e.mm(self.w_o, og, y, M)
+
+
 class RoutedExperts:
-    """Tensors <prefix>router, e<n>.up, e<n>.down.  Sizes: expert.ff, router {experts, top, groups {count, keep}}.
-    Router scores are sigmoid(W_router h) in f32; experts form `count` groups of neighbours scored by the sum of their
-    two largest scores, only the `keep` best groups are eligible; the `top` best eligible experts run and their outputs
-    are summed with their scores as weights (not renormalised)."""
+    """Tensors <prefix>router, e<n>.up, e<n>.down (gated experts: also e<n>.gate).  Sizes: expert.ff, router {experts,
+    top, groups {count, keep}, scale}, expert.limit.  Router logits are f32.  The design's `moe` traits:
+      score "sigmoid" (default): scores sigmoid(z); experts form `count` groups of neighbours scored by the sum of their
+            two largest scores, only the `keep` best groups are eligible;  "softmax": scores softmax(z) over all experts;
+      renorm: the chosen scores are divided by their sum (+ 1e-20); router.scale then multiplies the weights;
+      gated:  an expert is W_down (g sigmoid(1.702 g) (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit);
+              otherwise W_down relu(W_up h)^2.
+    The `top` best eligible experts run and their outputs are summed with the weights."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng = eng
+        tr = eng.cfg.traits.get("moe") or {}
+        self.softmax, self.renorm, self.gated = tr.get("score", "sigmoid") == "softmax", bool(tr.get("renorm")), bool(tr.get("gated"))
         r = m["router"]
         self.E, self.top, self.ff = int(r["experts"]), int(r["top"]), int(m["expert"]["ff"])
+        self.route_scale = float(r.get("scale") or 0.0)
+        self.limit = float(m["expert"].get("limit") or 0.0)
         g = r.get("groups") or {"count": 1, "keep": 1}
         self.groups, self.keep = int(g["count"]), int(g["keep"])
         if self.E % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.keep * (self.E // self.groups):
@@ -386,31 +517,36 @@ class RoutedExperts:
         self.router = eng.dense_weight(eng.weight(prefix + "router"))
         self.w_up = torch.stack([eng.weight(f"{prefix}e{n}.up") for n in range(self.E)]).contiguous()        # [E][ff][W]
         self.w_down = torch.stack([eng.weight(f"{prefix}e{n}.down") for n in range(self.E)]).contiguous()    # [E][W][ff]
-        if tuple(self.w_up.shape) != (self.E, self.ff, eng.cfg.width) or tuple(self.w_down.shape) != (self.E, eng.cfg.width, self.ff):
+        self.w_gate = torch.stack([eng.weight(f"{prefix}e{n}.gate") for n in range(self.E)]).contiguous() if self.gated else None
+        if tuple(self.w_up.shape) != (self.E, self.ff, eng.cfg.width) or tuple(self.w_down.shape) != (self.E, eng.cfg.width, self.ff) or \
+                (self.gated and self.w_gate.shape != self.w_up.shape):
             raise ValueError(f"layer {index}: expert weights have shapes {tuple(self.w_up.shape)} / {tuple(self.w_down.shape)}")
         # bf16 mode: batches of TC_MIN_ROWS rows and more sort their (row, expert) pairs by expert and run all experts as
         # one grouped tensor-core GEMM per projection; fewer rows stream the chosen experts' weights pair by pair
-        self.grouped = eng.L.MoeGrouped(self.w_up, self.w_down, self.top, eng.max_rows) if eng.tc else None
+        self.grouped = eng.L.MoeGrouped(self.w_up, self.w_down, self.top, eng.max_rows, w_gate=self.w_gate, limit=self.limit) if eng.tc else None
 
     def scratch(self) -> Dict[str, int]:
         return {"router_z": self.E, "moe_act": self.top * self.ff, "moe_sel": self.top, "moe_wgt": self.top}
 
     def weight_bytes(self) -> int:
-        return self.router.nbytes() + (self.w_up.numel() + self.w_down.numel()) * self.w_up.element_size()
+        n = self.w_up.numel() + self.w_down.numel() + (self.w_gate.numel() if self.gated else 0)
+        return self.router.nbytes() + n * self.w_up.element_size()
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
         e, L = self.eng, self.eng.L
         z, act = e.buf("router_z", self.E), e.buf("moe_act", self.top * self.ff)
         sel, wgt = e.buf("moe_sel", self.top).view(torch.int32), e.buf("moe_wgt", self.top)
         e.mm(self.router, h, z, M, src="h")
-        L.moe_select(z, M, self.E, self.top, self.groups, self.keep, sel, wgt)
+        L.moe_select(z, M, self.E, self.top, self.groups, self.keep, sel, wgt, renorm=self.renorm, softmax=self.softmax,
+                     scale=self.route_scale)
         if self.grouped is not None and M >= TC_MIN_ROWS:
             self.grouped.run(h, M, sel, wgt, y)
         else:
-            L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x)
+            L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x, w_gate=self.w_gate, limit=self.limit)
 
 
-MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer, "attention": WindowAttentionMixer}
+MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer, "attention": WindowAttentionMixer,
+          "lightning": LightningMixer}
 FEED_FORWARDS = {"dense": DenseFeedForward, "moe": RoutedExperts}
 
 
@@ -434,17 +570,25 @@ class _Layer:
         if spec.type not in MIXERS:
             raise ValueError(f"layer {i}: unknown mixer type {spec.type!r}")
         sandwich = eng.cfg.residual == "sandwich"
+        taps = eng.cfg.canon_taps
+        # the last taps - 1 inputs of the convolution in front of the mixer: every layer's own, per sequence slot
+        self.canon_state = torch.zeros(eng.n_slots, max(taps - 1, 1), eng.cfg.width, dtype=torch.float32, device=eng.device) if taps > 0 else None
         if owner is not None:
             # the owner's weights on a cache / state of this layer's own
-            if spec.type != "attention" or sandwich:
-                raise ValueError(f"layer {i}: weights_of is only known for attention mixers of hyper-style models")
+            if spec.type not in ("attention", "lightning") or sandwich:
+                raise ValueError(f"layer {i}: weights_of is only known for attention and lightning mixers of hyper-style models")
             self.mixer = MIXERS[spec.type](eng, i, spec.mixer, "", share=owner.mixer)
             self.ff = owner.ff
-            for n in ("norm1", "norm1b", "norm2", "norm2b", "hc1", "hc2"):
+            for n in ("norm1", "norm1b", "norm2", "norm2b", "hc1", "hc2", "canon1"):
                 setattr(self, n, getattr(owner, n, None))
             return
         self.mixer = MIXERS[spec.type](eng, i, spec.mixer, p + "mix.")
-        self.norm1 = eng.vector(p + "norm1")
+        self.norm1 = eng.norm_weight(p + "norm1")
+        self.canon1 = None
+        if taps > 0:
+            self.canon1 = eng.weight(p + "canon1")
+            if tuple(self.canon1.shape) != (eng.cfg.width, taps):
+                raise ValueError(f"layer {i}: canon1 has shape {tuple(self.canon1.shape)}")
         self.norm1b = eng.vector(p + "norm1b") if sandwich else None
         self.hc1 = self.hc2 = None
         if not sandwich:
@@ -455,7 +599,7 @@ class _Layer:
             if kind not in FEED_FORWARDS:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
             self.ff = FEED_FORWARDS[kind](eng, i, spec.mlp, p + "mlp.")
-            self.norm2 = eng.vector(p + "norm2")
+            self.norm2 = eng.norm_weight(p + "norm2")
             self.norm2b = eng.vector(p + "norm2b") if sandwich else None
             if not sandwich:
                 self.hc2 = _HyperWeights(eng, p + "hc2." if eng.cfg.hyper_weights else None)
@@ -509,7 +653,7 @@ class LayerListEngine:
                         raise ValueError(f"layer {i}: its entry differs from layer {spec.weights_of}, whose weights it uses")
                     built[i] = _Layer(self, i, spec, owner)
             self.layers: List[_Layer] = [built[i] for i in range(len(self.cfg.layers))]
-            self.final_norm, self.head = self.vector("final.norm"), self.dense_weight(self.weight("head"))
+            self.final_norm, self.head = self.norm_weight("final.norm"), self.dense_weight(self.weight("head"))
         finally:
             self._st.close()
         mixers = [l.mixer for l in self.layers]
@@ -540,6 +684,14 @@ class LayerListEngine:
                 torch.zeros(self._max_chunks * max(mx.H * mx.N * mx.P for mx in mam), dtype=torch.float32, device=dev),
                 torch.zeros(self._max_chunks * max(mx.H for mx in mam), dtype=torch.float32, device=dev),
                 torch.zeros(R * max(mx.H for mx in mam), dtype=torch.float32, device=dev))
+        # linear attention: portions of LIGHTNING_CHUNKED_MIN_ROWS rows and more run chunk-parallel (three launches)
+        lt = [mx for mx in mixers if isinstance(mx, LightningMixer) and mx.chunked]
+        self.lightning_chunks, self._lightning_scratch = 0, None
+        if lt and R >= LIGHTNING_CHUNKED_MIN_ROWS and os.environ.get("DLLAMA_LAYERS_CHUNKED_SCAN", "1") != "0":
+            self._lightning_scratch = torch.zeros(max(L.lightning_chunk_floats(R, self.n_slots, mx.H, mx.dim, mx.vdim) for mx in lt),
+                                                  dtype=torch.float32, device=dev)
+        if self.cfg.canon_taps and self.cfg.residual == "sandwich":
+            raise ValueError("a convolution in front of the mixers is only wired into the pre-norm / hyper residual style")
         # scratch: one f32 buffer per name, as wide as the widest user
         widths: Dict[str, int] = {}
         for l in self.layers:
@@ -558,6 +710,7 @@ class LayerListEngine:
             raise ValueError(f"{self.cfg.streams} streams: the kernels keep at most {L.HC_MAX_STREAMS} copies of the residual stream")
         self.x = torch.zeros(R, self.cfg.streams * self.cfg.width, dtype=torch.float32, device=dev)      # row = [streams][width]
         self.hn = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
+        self.hc = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev) if self.cfg.canon_taps else None
         self.y = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
         self.logits = torch.zeros(R, self.cfg.vocab, dtype=torch.float32, device=dev)
         self.out_tokens = torch.zeros(R, dtype=torch.int32, device=dev)
@@ -617,6 +770,16 @@ class LayerListEngine:
             raise KeyError(f"model.safetensors has no tensor {name!r}")
         return self._st.tensor(name).to(torch.float32).to(self.device).contiguous()
 
+    def norm_weight(self, name: str) -> torch.Tensor:
+        """The weight of a norm over the model's width: a vector, or one number for all coordinates (stored as a tensor
+        without dimensions), which is widened here."""
+        w = self.vector(name)
+        if w.numel() == 1:
+            return w.reshape(1).expand(self.cfg.width).contiguous()
+        if tuple(w.shape) != (self.cfg.width,):
+            raise ValueError(f"{name} has shape {tuple(w.shape)}")
+        return w
+
     def dense_weight(self, t: torch.Tensor) -> DenseWeight:
         self._kmax = max(self._kmax, int(t.shape[-1]))
         return DenseWeight(t, self.tc)
@@ -651,6 +814,9 @@ class LayerListEngine:
         if not self._n_chunks or not self.L.mamba_chunked_supported(mx.P, mx.N):
             return None
         return (self.chunk_seq, self.chunk_off, self._n_chunks) + self._chunk_scratch
+
+    def lightning_scratch(self, mx):
+        return self._lightning_scratch
 
     def latent_tiles(self, mx):
         """The row tiling of this batch for the tensor-core attention kernel, or None where the per-row kernel runs."""
@@ -756,8 +922,12 @@ class LayerListEngine:
                     hd[wo + nt * rq + len(part):wo + (nt + 1) * rq] = -1
                     nt += 1
             self._wtile_n[rq] = nt
+        longest = max(len(r) for r in by_slot.values())
+        self.lightning_chunks = 0
+        if self._lightning_scratch is not None and longest >= LIGHTNING_CHUNKED_MIN_ROWS:
+            self.lightning_chunks = (longest + self.L.LIGHTNING_CHUNK - 1) // self.L.LIGHTNING_CHUNK
         self._n_chunks = 0
-        if self._chunk_scratch is not None and max(len(r) for r in by_slot.values()) >= CHUNKED_SCAN_MIN_ROWS:
+        if self._chunk_scratch is not None and longest >= CHUNKED_SCAN_MIN_ROWS:
             co, nc, ch = self._chunks_off, 0, self.L.MAMBA_CHUNK
             for n, rows in enumerate(by_slot.values()):
                 for off in range(0, len(rows), ch):
@@ -824,7 +994,11 @@ class LayerListEngine:
                     L.hyper_step(x, M, S, W, y=y, mix=pending.mix, w_out=pending.w_out, mult=mult,
                                  h=hn, w_in=hc.w_in, norm_w=norm, eps=eps)
                 self.begin_sublayer()
-                sub.forward(hn, y, M)
+                if sub is l.mixer and l.canon1 is not None:      # h <- h + conv(h) over the sequence's last inputs
+                    L.causal_conv(self.mamba_batch, M, self.n_seq, hn, l.canon1, l.canon_state, self.hc, residual=True)
+                    sub.forward(self.hc, y, M)
+                else:
+                    sub.forward(hn, y, M)
                 pending = hc
             if self.layer_probe is not None:
                 L.hyper_step(x, M, S, W, y=y, mix=pending.mix, w_out=pending.w_out, mult=mult)
@@ -918,9 +1092,18 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
         return (torch.randn(n, generator=g) * s).to(torch.bfloat16)
 
     sandwich = RESIDUAL_STYLES.get(config["architecture"], "sandwich") == "sandwich"
+    traits = DESIGNS.get(config["architecture"], {})
+    att, moe = traits.get("attention") or {}, traits.get("moe") or {}
+    taps = int((config.get("canon") or {}).get("taps") or 0)
     S = int(config.get("streams") or 0)
-    t = {"embed": (torch.randn(V, W, generator=g)).to(torch.bfloat16), "head": mat(V, W),
-         "final.norm": small(W) if sandwich else 1 + small(W)}
+    scalar_norms = config["architecture"] == "Venadra"          # one number per norm
+
+    def norm_w():
+        if scalar_norms:
+            return (1 + torch.randn((), generator=g) * 0.1).to(torch.bfloat16)
+        return small(W) if sandwich else 1 + small(W)
+
+    t = {"embed": (torch.randn(V, W, generator=g)).to(torch.bfloat16), "head": mat(V, W), "final.norm": norm_w()}
 
     def hyper(prefix):
         # read weights around 1 / S, write weights around 1, a mixing matrix near the identity with some cross-talk
@@ -932,7 +1115,9 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
         p, m = f"l{i}.", l["mixer"]
         if l.get("weights_of") is not None:
             continue
-        t[p + "norm1"] = small(W) if sandwich else 1 + small(W)
+        t[p + "norm1"] = norm_w()
+        if taps:
+            t[p + "canon1"] = mat(W, taps, 0.5)
         if sandwich:
             t[p + "norm1b"] = small(W)
         elif S:
@@ -955,12 +1140,22 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             t[p + "mix.D"], t[p + "mix.norm"] = 1 + small(H), 1 + small(inner)
             t[p + "mix.o"] = mat(W, inner)
         elif l["type"] == "attention":
-            H, G, d = m["heads"], m["kv_heads"], m["dim"]
-            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.o"] = mat(H * d, W, 2.0), mat(G * d, W, 2.0), mat(W, H * d)
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.o"] = mat(H * d, W, 2.0), mat(G * d, W, 2.0), mat(W, H * dv)
+            if att.get("values") == "own":
+                t[p + "mix.v"] = mat(G * dv, W)
+            if att.get("sink"):
+                t[p + "mix.sink"] = (torch.randn(H, generator=g)).to(torch.bfloat16)
+            if att.get("gate"):
+                t[p + "mix.g"] = mat(H * dv, W)
+        elif l["type"] == "lightning":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(H * d, W, 2.0), mat(H * d, W, 2.0), mat(H * dv, W, 2.0)
+            t[p + "mix.g"], t[p + "mix.o"], t[p + "mix.norm"] = mat(H * dv, W), mat(W, H * dv), 1 + small(H * dv)
         else:
             raise ValueError(f"layer {i}: unknown mixer type {l['type']!r}")
         if l.get("mlp"):
-            t[p + "norm2"] = small(W) if sandwich else 1 + small(W)
+            t[p + "norm2"] = norm_w()
             if sandwich:
                 t[p + "norm2b"] = small(W)
             elif S:
@@ -970,8 +1165,12 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
                 t[p + "mlp.router"] = mat(E, W, 2.0)
                 for n in range(E):
                     t[p + f"mlp.e{n}.up"], t[p + f"mlp.e{n}.down"] = mat(ff, W, 1.5), mat(W, ff)
+                    if moe.get("gated"):
+                        t[p + f"mlp.e{n}.gate"] = mat(ff, W, 1.5)
             else:
                 t[p + "mlp.up"], t[p + "mlp.down"] = mat(l["mlp"]["ff"], W), mat(W, l["mlp"]["ff"])
+                if traits.get("dense_act") == "polynorm":
+                    t[p + "mlp.act"] = torch.tensor([0.6, 0.3, 0.15, 0.05]).add(torch.randn(4, generator=g) * 0.05).to(torch.bfloat16)
     return t
 
 
@@ -1018,3 +1217,19 @@ def example_config_sunesun(width: int = 160, vocab: int = 320, layers: int = 3, 
         return l
     return {"architecture": "Sunesun", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
             "residual_mult": 0.5, "streams": streams, "layers": [layer(i) for i in range(layers)]}
+
+
+def example_config_venadra(width: int = 160, vocab: int = 320, heads: int = 3, chunk: int = 40) -> dict:
+    """A small Venadra-shaped configuration: lightning layers (dense PolyNorm and gated-expert feed-forwards), one chunked
+    sink-attention layer, a 3-tap convolution in front of every mixer; the last two layers run earlier layers' weights."""
+    light = {"heads": heads, "dim": 16, "vdim": 24, "decay": [round(0.5 + 0.499 * i / max(heads - 1, 1), 4) for i in range(heads)]}
+    attn = {"heads": 2 * heads, "kv_heads": heads, "dim": 32, "vdim": 32, "scale": 0.2, "mask": {"size": chunk}}
+    dense = {"kind": "dense", "ff": 2 * width}
+    moe = {"kind": "moe", "expert": {"ff": 48, "limit": 1.5}, "router": {"experts": 6, "top": 2, "scale": 1.25}}
+    layers = [{"type": "lightning", "mixer": dict(light), "mlp": dict(dense)},
+              {"type": "attention", "mixer": dict(attn), "mlp": dict(moe)},
+              {"type": "lightning", "mixer": dict(light), "mlp": dict(moe)},
+              {"type": "lightning", "mixer": dict(light), "mlp": dict(dense), "weights_of": 0},
+              {"type": "attention", "mixer": dict(attn), "mlp": dict(moe), "weights_of": 1}]
+    return {"architecture": "Venadra", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 4.0},
+            "canon": {"taps": 3}, "layers": layers}

@@ -20,6 +20,7 @@ def _layer_list(*args, **kw):
 ARCHITECTURES: Dict[str, Callable] = {
     "Ribivik": _layer_list,        # mamba2 and latent_attention mixers in the order its configuration lists
     "Sunesun": _layer_list,        # windowed attention (values = keys) + routed experts on hyper-connected residual streams
+    "Venadra": _layer_list,        # lightning (linear) attention and chunked sink attention behind a short convolution, PolyNorm / gated experts
 }
 
 

@@ -10,8 +10,8 @@ from typing import Optional
 import torch
 
 from . import lib
-from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
-                  DlEpilogue, DlHyperArgs, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlMoeArgs,
+from .lib import (DENSE_GLU_CLAMP, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SILU, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32,  # noqa: F401
+                  DlConvArgs, DlDenseArgs, DlEpilogue, DlHyperArgs, DlLatentAttnArgs, DlLightningArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlMoeArgs,
                   DlMoePlanArgs, DlMoeSelectArgs, DlNormArgs, DlWindowAttnArgs, DlWindowKvArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
@@ -128,6 +128,14 @@ def rms_norm(x: torch.Tensor, y: torch.Tensor, M: int, dim: int, eps: float, w: 
     lib.count_launch()
 
 
+def poly_norm(x: torch.Tensor, y: torch.Tensor, M: int, dim: int, coef: torch.Tensor, eps: float):
+    """y = c0 N(x) + c1 N(x^2) + c2 N(x^3) + c3 per row, N(u) = u / sqrt(mean(u^2) + eps); coef: 4 f32 on the device."""
+    assert coef.dtype == torch.float32 and coef.numel() == 4
+    check_layers(layers_lib().dl_poly_norm(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), M, dim, coef.data_ptr(), eps, _stream()),
+                 "dl_poly_norm")
+    lib.count_launch()
+
+
 def latent_kv_write(kv: torch.Tensor, M: int, norm_w: torch.Tensor, eps: float, rank: int, rot: int, rope_dims: int,
                     freqs: torch.Tensor, pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
     a = DlLatentKvArgs()
@@ -200,6 +208,49 @@ def mamba_conv(batch: DlMambaBatch, M: int, n_seq: int, zx: torch.Tensor, in_off
     lib.count_launch(2 if taps > 1 else 1)
 
 
+def causal_conv(batch: DlMambaBatch, M: int, n_seq: int, x: torch.Tensor, w: torch.Tensor, conv_state: torch.Tensor,
+                out: torch.Tensor, bias: Optional[torch.Tensor] = None, act: bool = False, residual: bool = False, in_off: int = 0):
+    """out[m][ch] = act(bias + sum_k w[ch][k] x[position - (taps - 1) + k][ch]) (+ x[m][ch]); zeros before a sequence's
+    start; conv_state [slots][taps - 1][channels] carries every slot's last inputs and is updated."""
+    channels, taps = w.shape
+    a = DlConvArgs()
+    a.in_, a.ld, a.in_off = x.data_ptr(), x.stride(0), in_off
+    a.w, a.bias, a.wtype, a.conv_state = w.data_ptr(), _p(bias), _type(w), conv_state.data_ptr()
+    a.out, a.ld_out = out.data_ptr(), out.stride(0)
+    a.channels, a.taps, a.act, a.residual = channels, taps, 1 if act else 0, 1 if residual else 0
+    check_layers(layers_lib().dl_causal_conv(batch, M, n_seq, a, _stream()), "dl_causal_conv")
+    lib.count_launch(2 if taps > 1 else 1)
+
+
+LIGHTNING_CHUNK = 64         # DL_LIGHTNING_CHUNK: rows of a sequence per chunk of the chunked linear-attention scan
+
+
+def lightning_chunked_supported(dim: int, vdim: int) -> bool:
+    return layers_lib().dl_lightning_scan_chunked_supported(dim, vdim) == 0
+
+
+def lightning_chunk_floats(M: int, n_seq: int, n_heads: int, dim: int, vdim: int) -> int:
+    return int(layers_lib().dl_lightning_chunk_floats(M, n_seq, n_heads, dim, vdim))
+
+
+def lightning_scan(batch: DlMambaBatch, n_seq: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
+                   y: torch.Tensor, state: torch.Tensor, n_heads: int, dim: int, vdim: int, max_chunks: int = 0,
+                   scratch: Optional[torch.Tensor] = None):
+    """Linear attention with a decay per head: S <- decay S + k v^T, y = S^T q per row, state [slots][heads][dim][vdim] f32.
+    max_chunks > 0 (with scratch): the chunk-parallel form for long portions."""
+    a = DlLightningArgs()
+    a.q, a.k, a.v, a.ldq, a.ldk, a.ldv = q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0)
+    a.decay, a.y, a.ld_y, a.state = decay.data_ptr(), y.data_ptr(), y.stride(0), state.data_ptr()
+    a.n_heads, a.dim, a.vdim = n_heads, dim, vdim
+    if max_chunks > 0:
+        check_layers(layers_lib().dl_lightning_scan_chunked(batch, n_seq, max_chunks, a, scratch.data_ptr(), _stream()),
+                     "dl_lightning_scan_chunked")
+        lib.count_launch(3)
+        return
+    check_layers(layers_lib().dl_lightning_scan(batch, n_seq, a, _stream()), "dl_lightning_scan")
+    lib.count_launch()
+
+
 MAMBA_CHUNK = 128            # rows of a sequence per chunk of the chunked scan
 
 
@@ -246,9 +297,11 @@ def hyper_step(x: torch.Tensor, M: int, streams: int, dim: int, y: Optional[torc
 
 # ---- sliding-window attention whose values are its keys ---------------------------------------------------------------
 def window_kv_write(k: torch.Tensor, M: int, kv_heads: int, dim: int, rope_dims: int, freqs: torch.Tensor, rope_scale: float,
-                    pos, slot, block_table: torch.Tensor, cache: torch.Tensor, q: Optional[torch.Tensor] = None, q_heads: int = 0):
+                    pos, slot, block_table: torch.Tensor, cache: torch.Tensor, q: Optional[torch.Tensor] = None, q_heads: int = 0,
+                    v: Optional[torch.Tensor] = None, vdim: int = 0, qk_norm: bool = False, eps: float = 0.0):
     """Keys into the paged cache (rotated key + unrotated head per line); with q [M][q_heads * dim] the queries are
-    rotated in place by the same launch."""
+    rotated in place by the same launch.  With v [M][kv_heads * vdim] (no rotary) the line is key + value, and qk_norm
+    divides every query and key head by its root mean square first."""
     a = DlWindowKvArgs()
     a.k, a.ld, a.kv_heads, a.dim, a.rope_dims = k.data_ptr(), k.stride(0), kv_heads, dim, rope_dims
     a.q, a.ldq, a.q_heads = _p(q), (q.stride(0) if q is not None else 0), q_heads
@@ -256,11 +309,14 @@ def window_kv_write(k: torch.Tensor, M: int, kv_heads: int, dim: int, rope_dims:
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
     a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
     a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    a.v, a.ldv, a.vdim = _p(v), (v.stride(0) if v is not None else 0), vdim
+    a.qk_norm, a.eps = 1 if qk_norm else 0, eps
     check_layers(layers_lib().dl_window_kv_write(a, M, _stream()), "dl_window_kv_write")
     lib.count_launch()
 
 
-def _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache):
+def _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache,
+                 vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None):
     a = DlWindowAttnArgs()
     a.q, a.ldq, a.out, a.ldo = q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0)
     a.heads, a.kv_heads, a.dim, a.rope_dims = heads, kv_heads, dim, rope_dims
@@ -268,13 +324,16 @@ def _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
     a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
     a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    a.vdim, a.chunk, a.sink = vdim, chunk, _p(sink)
     return a
 
 
 def window_attention(q: torch.Tensor, out: torch.Tensor, M: int, heads: int, kv_heads: int, dim: int, rope_dims: int,
-                     scale: float, softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
-    """The per-row kernel (either cache type, f32 arithmetic)."""
-    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache)
+                     scale: float, softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor,
+                     vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None):
+    """The per-row kernel (either cache type, f32 arithmetic).  vdim > 0: values of their own behind the keys; chunk > 0:
+    only keys of the row's own chunk of positions are visible; sink [heads]: joins the softmax denominator."""
+    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, vdim, chunk, sink)
     check_layers(layers_lib().dl_window_attention(a, M, _stream()), "dl_window_attention")
     lib.count_launch()
 
@@ -295,10 +354,11 @@ def window_tc_partial_floats(n_tiles: int, kv_heads: int, n_splits: int, dim: in
 
 def window_attention_tc(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, rope_dims: int, scale: float,
                         softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor,
-                        tile_rows: torch.Tensor, n_tiles: int, rq: int, n_splits: int = 1, partial: Optional[torch.Tensor] = None):
+                        tile_rows: torch.Tensor, n_tiles: int, rq: int, n_splits: int = 1, partial: Optional[torch.Tensor] = None,
+                        vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None):
     """The tensor-core kernel over row tiles (tile_rows int32 [n_tiles][rq] on the device, -1 = no row).  n_splits > 1:
     that many CTAs share each tile's pages (few tiles: decoding) and a merge launch follows; partial: f32 scratch."""
-    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache)
+    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, vdim, chunk, sink)
     if n_splits > 1:
         assert partial is not None and partial.numel() >= window_tc_partial_floats(n_tiles, kv_heads, n_splits, dim)
     check_layers(layers_lib().dl_window_attention_tc(a, tile_rows.data_ptr(), n_tiles, rq, n_splits, _p(partial), _stream()),
@@ -307,7 +367,7 @@ def window_attention_tc(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads
 
 
 def window_attention_tiles(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, tiles,
-                           n_splits: int = 1):
+                           n_splits: int = 1, vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None):
     """Convenience for callers with host-side tiles (lists of row indices of one sequence, consecutive positions)."""
     rq = window_tc_rows(heads, kv_heads)
     t = torch.full((len(tiles), rq), -1, dtype=torch.int32)
@@ -317,27 +377,32 @@ def window_attention_tiles(q, out, heads, kv_heads, dim, rope_dims, scale, softc
     if n_splits > 1:
         partial = torch.zeros(window_tc_partial_floats(len(tiles), kv_heads, n_splits, dim), dtype=torch.float32, device=q.device)
     window_attention_tc(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache,
-                        t.to(q.device), len(tiles), rq, n_splits, partial)
+                        t.to(q.device), len(tiles), rq, n_splits, partial, vdim, chunk, sink)
 
 
 # ---- routed experts ---------------------------------------------------------------------------------------------------
 def moe_select(z: torch.Tensor, M: int, experts: int, top: int, groups: int, keep: int, sel: torch.Tensor, wgt: torch.Tensor,
-               group_top: int = 2, renorm: bool = False):
+               group_top: int = 2, renorm: bool = False, softmax: bool = False, scale: float = 0.0):
+    """sel / wgt [M][top]: the chosen experts and their weights.  Scores: sigmoid(z), or softmax(z) over all experts;
+    renorm divides the chosen scores by their sum (+ 1e-20); scale (0: none) multiplies the weights."""
     a = DlMoeSelectArgs()
     a.z, a.ldz, a.M, a.experts, a.top, a.groups, a.keep = z.data_ptr(), z.stride(0), M, experts, top, groups, keep
     a.group_top, a.renorm, a.sel, a.wgt = group_top, 1 if renorm else 0, sel.data_ptr(), wgt.data_ptr()
+    a.score, a.scale = 1 if softmax else 0, scale
     check_layers(layers_lib().dl_moe_select(a, _stream()), "dl_moe_select")
     lib.count_launch()
 
 
 def moe_rows(w_up: torch.Tensor, w_down: torch.Tensor, x: torch.Tensor, M: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
-             act: torch.Tensor, y: torch.Tensor, round_x: bool):
-    """w_up [experts][ff][width], w_down [experts][width][ff]; one product per (row, chosen expert) pair."""
+             act: torch.Tensor, y: torch.Tensor, round_x: bool, w_gate: Optional[torch.Tensor] = None, limit: float = 0.0):
+    """w_up [experts][ff][width], w_down [experts][width][ff]; one product per (row, chosen expert) pair.  With w_gate
+    (like w_up) the experts are gated: g sigmoid(1.702 g) (u + 1) on the products clamped by `limit`, else relu(u)^2."""
     a = DlMoeArgs()
     a.w_up, a.w_down, a.wtype = w_up.data_ptr(), w_down.data_ptr(), _type(w_up)
     a.width, a.ff, a.top, a.M, a.round_x = w_up.shape[2], w_up.shape[1], top, M, 1 if round_x else 0
     a.x, a.ldx, a.sel, a.wgt = x.data_ptr(), x.stride(0), sel.data_ptr(), wgt.data_ptr()
     a.act, a.y, a.ldy = act.data_ptr(), y.data_ptr(), y.stride(0)
+    a.w_gate, a.limit = _p(w_gate), limit
     check_layers(layers_lib().dl_moe_rows(a, _stream()), "dl_moe_rows")
     lib.count_launch(2)
 
@@ -347,16 +412,24 @@ class MoeGrouped:
     scratch of the sorted rows, and the launch sequence  plan -> gather -> grouped GEMM (relu^2) -> image -> grouped GEMM
     -> weighted combine.  Nothing returns to the host between the launches."""
 
-    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, top: int, max_rows: int):
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, top: int, max_rows: int, w_gate: Optional[torch.Tensor] = None,
+                 limit: float = 0.0):
         Lb = layers_lib()
         self.E, self.ff, self.width, self.top = w_up.shape[0], w_up.shape[1], w_up.shape[2], top
         dev = w_up.device
-        self.up_bytes = int(Lb.dl_wh_bytes(self.ff, _round_up(self.width, 128)))
+        # gated experts: gate and up rows interleaved (gate_0, up_0, gate_1, ...) in ONE image of 2 ff rows, so the first
+        # grouped GEMM's epilogue sees a value's two products side by side and stores the activation
+        self.gated, self.limit = w_gate is not None, limit
+        self.n_up = self.ff
+        if self.gated:
+            w_up = torch.stack([w_gate, w_up], dim=2).reshape(self.E, 2 * self.ff, self.width).contiguous()
+            self.n_up = 2 * self.ff
+        self.up_bytes = int(Lb.dl_wh_bytes(self.n_up, _round_up(self.width, 128)))
         self.down_bytes = int(Lb.dl_wh_bytes(self.width, _round_up(self.ff, 128)))
         self.wh_up = torch.empty(self.E * self.up_bytes, dtype=torch.uint8, device=dev)
         self.wh_down = torch.empty(self.E * self.down_bytes, dtype=torch.uint8, device=dev)
         for e in range(self.E):
-            check_layers(Lb.dl_wh_from_dense(w_up[e].data_ptr(), self.ff, self.width, w_up.stride(1),
+            check_layers(Lb.dl_wh_from_dense(w_up[e].data_ptr(), self.n_up, self.width, w_up.stride(1),
                                              self.wh_up[e * self.up_bytes:].data_ptr(), _stream()), "dl_wh_from_dense")
             check_layers(Lb.dl_wh_from_dense(w_down[e].data_ptr(), self.width, self.ff, w_down.stride(1),
                                              self.wh_down[e * self.down_bytes:].data_ptr(), _stream()), "dl_wh_from_dense")
@@ -373,11 +446,11 @@ class MoeGrouped:
     def nbytes(self) -> int:
         return self.wh_up.numel() + self.wh_down.numel()
 
-    def _gemm(self, wh, group_bytes, N, K, xh, y, M, epi):
+    def _gemm(self, wh, group_bytes, N, K, xh, y, M, epi, param=0.0):
         e = DlEpilogue()
         e.kind, e.n_dst, e.ld, e.dst_off = EPI_DENSE, 1, y.stride(0), 0
         e.dst[0] = y.data_ptr()
-        e.dense_op, e.dense_param, e.dense_aux, e.dense_aux_ld = epi, 0.0, None, 0
+        e.dense_op, e.dense_param, e.dense_aux, e.dense_aux_ld = epi, param, None, 0
         check_layers(layers_lib().dl_gemm_wh_tc_grouped(wh.data_ptr(), group_bytes, self.E, self.grp.data_ptr(), N, _round_up(K, 128),
                                                         xh.data_ptr(), self.cap, M, e, 2, _stream()), "dl_gemm_wh_tc_grouped")
         lib.count_launch()
@@ -393,7 +466,10 @@ class MoeGrouped:
         check_layers(Lb.dl_moe_plan(a, _stream()), "dl_moe_plan")
         check_layers(Lb.dl_xh_gather_rows(x.data_ptr(), x.stride(0), self.slot_row.data_ptr(), n_sorted, self.width, self.cap,
                                           self.xh_in.data_ptr(), _stream()), "dl_xh_gather_rows")
-        self._gemm(self.wh_up, self.up_bytes, self.ff, self.width, self.xh_in, self.act, M, DENSE_RELU2)
+        if self.gated:
+            self._gemm(self.wh_up, self.up_bytes, self.n_up, self.width, self.xh_in, self.act, M, DENSE_GLU_CLAMP, self.limit)
+        else:
+            self._gemm(self.wh_up, self.up_bytes, self.ff, self.width, self.xh_in, self.act, M, DENSE_RELU2)
         check_layers(Lb.dl_xh_from_rows(self.act.data_ptr(), self.act.stride(0), n_sorted, self.ff, self.cap, self.xh_act.data_ptr(),
                                         _stream()), "dl_xh_from_rows")
         self._gemm(self.wh_down, self.down_bytes, self.width, self.ff, self.xh_act, self.yp, M, DENSE_STORE)

@@ -166,6 +166,14 @@ def cuda_lib():
     L.dl_gemv_q40_smem_bytes.restype = i64
     L.dl_gemv_q40_smem_bytes.argtypes = [i32, i32, i32]
     L.dl_gemm_q40_tc.argtypes = [vp, i32, i32, vp, i32, i32, i32, C.POINTER(DlEpilogue), i32, vp]
+    L.dl_causal_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, C.POINTER(DlConvArgs), vp]
+    L.dl_poly_norm.argtypes = [vp, i64, vp, i64, i32, i32, vp, C.c_float, vp]
+    L.dl_lightning_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlLightningArgs), vp]
+    L.dl_lightning_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), i32, i32, C.POINTER(DlLightningArgs), vp, vp]
+    L.dl_lightning_scan_chunked_supported.argtypes = [i32, i32]
+    L.dl_lightning_scan_chunked_supported.restype = i32
+    L.dl_lightning_chunk_floats.argtypes = [i32, i32, i32, i32, i32]
+    L.dl_lightning_chunk_floats.restype = i64
     L.dl_wh_bytes.restype = i64
     L.dl_wh_bytes.argtypes = [i32, i32]
     L.dl_q40t_to_wh.argtypes = [vp, i32, i32, vp, vp]
@@ -213,7 +221,7 @@ def check(rc: int, what: str = ""):
 # ---- libdllama_b200_layers.so: kernels of layer-list models (dense weights, latent and windowed attention, Mamba-2,
 # ---- hyper-connections, routed experts)
 T_F32, T_BF16 = 0, 1
-DENSE_STORE, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP = 0, 1, 2, 3
+DENSE_STORE, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_SILU, DENSE_GLU_CLAMP = 0, 1, 2, 3, 4, 5
 
 
 class DlDenseArgs(C.Structure):
@@ -292,7 +300,8 @@ class DlWindowKvArgs(C.Structure):
                 ("kv_heads", C.c_int), ("dim", C.c_int), ("rope_dims", C.c_int),
                 ("freqs", C.c_void_p), ("rope_scale", C.c_float),
                 ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
-                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
+                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int),
+                ("v", C.c_void_p), ("ldv", C.c_longlong), ("vdim", C.c_int), ("qk_norm", C.c_int), ("eps", C.c_float)]
 
 
 class DlWindowAttnArgs(C.Structure):
@@ -301,14 +310,31 @@ class DlWindowAttnArgs(C.Structure):
                 ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("rope_dims", C.c_int),
                 ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
                 ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
-                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
+                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int),
+                ("vdim", C.c_int), ("chunk", C.c_int), ("sink", C.c_void_p)]
+
+
+class DlConvArgs(C.Structure):
+    """Mirror of ``DlConvArgs``."""
+    _fields_ = [("in_", C.c_void_p), ("ld", C.c_longlong), ("in_off", C.c_int),
+                ("w", C.c_void_p), ("bias", C.c_void_p), ("wtype", C.c_int), ("conv_state", C.c_void_p),
+                ("out", C.c_void_p), ("ld_out", C.c_longlong),
+                ("channels", C.c_int), ("taps", C.c_int), ("act", C.c_int), ("residual", C.c_int)]
+
+
+class DlLightningArgs(C.Structure):
+    """Mirror of ``DlLightningArgs``."""
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+                ("ldq", C.c_longlong), ("ldk", C.c_longlong), ("ldv", C.c_longlong),
+                ("decay", C.c_void_p), ("y", C.c_void_p), ("ld_y", C.c_longlong), ("state", C.c_void_p),
+                ("n_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int)]
 
 
 class DlMoeSelectArgs(C.Structure):
     """Mirror of ``DlMoeSelectArgs``."""
     _fields_ = [("z", C.c_void_p), ("ldz", C.c_longlong), ("M", C.c_int), ("experts", C.c_int), ("top", C.c_int),
                 ("groups", C.c_int), ("keep", C.c_int), ("group_top", C.c_int), ("renorm", C.c_int),
-                ("sel", C.c_void_p), ("wgt", C.c_void_p)]
+                ("sel", C.c_void_p), ("wgt", C.c_void_p), ("score", C.c_int), ("scale", C.c_float)]
 
 
 class DlMoeArgs(C.Structure):
@@ -316,7 +342,7 @@ class DlMoeArgs(C.Structure):
     _fields_ = [("w_up", C.c_void_p), ("w_down", C.c_void_p), ("wtype", C.c_int),
                 ("width", C.c_int), ("ff", C.c_int), ("top", C.c_int), ("M", C.c_int), ("round_x", C.c_int),
                 ("x", C.c_void_p), ("ldx", C.c_longlong), ("sel", C.c_void_p), ("wgt", C.c_void_p),
-                ("act", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong)]
+                ("act", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong), ("w_gate", C.c_void_p), ("limit", C.c_float)]
 
 
 class DlMoePlanArgs(C.Structure):
@@ -370,6 +396,14 @@ def layers_lib():
     L.dl_mamba_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), C.POINTER(DlMambaScanArgs), C.POINTER(DlMambaChunks), vp]
     L.dl_mamba_scan_chunked_supported.argtypes = [i32, i32]
     L.dl_mamba_scan_chunked_supported.restype = i32
+    L.dl_causal_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, C.POINTER(DlConvArgs), vp]
+    L.dl_poly_norm.argtypes = [vp, i64, vp, i64, i32, i32, vp, C.c_float, vp]
+    L.dl_lightning_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlLightningArgs), vp]
+    L.dl_lightning_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), i32, i32, C.POINTER(DlLightningArgs), vp, vp]
+    L.dl_lightning_scan_chunked_supported.argtypes = [i32, i32]
+    L.dl_lightning_scan_chunked_supported.restype = i32
+    L.dl_lightning_chunk_floats.argtypes = [i32, i32, i32, i32, i32]
+    L.dl_lightning_chunk_floats.restype = i64
     L.dl_wh_bytes.restype = i64
     L.dl_wh_bytes.argtypes = [i32, i32]
     L.dl_wh_from_dense.argtypes = [vp, i32, i32, i64, vp, vp]
@@ -383,7 +417,7 @@ def layers_lib():
                  "dl_mamba_conv", "dl_mamba_scan", "dl_mamba_scan_chunked", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
                  "dl_gemm_wh_tc", "dl_hyper_step", "dl_window_kv_write", "dl_window_attention", "dl_moe_select", "dl_moe_rows", "dl_moe_plan",
                  "dl_moe_combine", "dl_xh_gather_rows", "dl_gemm_wh_tc_grouped", "dl_window_tc_rows", "dl_window_attention_tc_supported",
-                 "dl_window_attention_tc"):
+                 "dl_window_attention_tc", "dl_causal_conv", "dl_poly_norm", "dl_lightning_scan", "dl_lightning_scan_chunked"):
         getattr(L, name).restype = i32
     _layers = L
     return L

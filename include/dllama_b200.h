@@ -24,7 +24,8 @@ enum {
     DL_EPI_DENSE = 3,     /* f32 store to dst[0] through one of the DL_DENSE_* element-wise ops      */
 };
 /* element-wise ops on a matmul result (dense-weight models): store, relu(.)^2, aux * sigmoid(.), param * tanh(. / param) */
-enum { DL_DENSE_STORE = 0, DL_DENSE_RELU2 = 1, DL_DENSE_SIGMOID_MUL = 2, DL_DENSE_SOFTCAP = 3 };
+enum { DL_DENSE_STORE = 0, DL_DENSE_RELU2 = 1, DL_DENSE_SIGMOID_MUL = 2, DL_DENSE_SOFTCAP = 3, DL_DENSE_SILU = 4,
+       DL_DENSE_GLU_CLAMP = 5 /* tensor-core epilogue only: output columns (2j, 2j+1) = (gate, up) of value j, see DlMoeArgs */ };
 
 typedef struct {
     int kind;
@@ -312,7 +313,7 @@ int dl_peer_barrier(uint32_t* const* flags_on_peers /*host array*/, uint32_t* my
 
 /* Y[b][m][n] = epi( sum_k X[b][m][k] * W[b][n][k] ),  b < batch (element strides *_bs).  round_x: the activation
  * operand is rounded to bf16 on load (bf16 mode).  DL_DENSE_SIGMOID_MUL: aux[m][n] * sigmoid(.);
- * DL_DENSE_SOFTCAP: param * tanh(. / param). */
+ * DL_DENSE_SOFTCAP: param * tanh(. / param); DL_DENSE_SILU: . * sigmoid(.). */
 typedef struct {
     const void* W; int wtype; long long ldw, w_bs;
     const float* X; long long ldx, x_bs;
@@ -347,6 +348,10 @@ typedef struct {
     int plus_one, accumulate;
 } DlNormArgs;
 int dl_rms_norm(const DlNormArgs* args /*host*/, void* stream);
+/* y[m] = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 with z = x[m], powers element-wise, N(u) = u / sqrt(mean(u^2) + eps);
+ * coef: 4 f32 on the device.  In place is allowed. */
+int dl_poly_norm(const float* x, long long ldx, float* y, long long ldy, int M, int dim, const float* coef, float eps,
+                 void* stream);
 
 /* latent-attention cache writer: row m of kv[M][ld] = [rank | rot]; the first `rank` are RMS-normed (* norm_w), the
  * first rope_dims of the last `rot` are rotated by the row's position (freqs: f64 [rope_dims / 2]); the token's
@@ -405,6 +410,16 @@ typedef struct {
 int dl_mamba_conv(const DlMambaBatch* batch /*host*/, int M, int n_seq, const float* in, long long ld, int in_off,
                   const void* w, const void* bias, int wtype, float* conv_state, float* out, int channels, int taps,
                   void* stream);
+/* The general form: out[m][ch] = act(bias[ch] + conv) (+ in[m][ch] if residual); bias may be NULL; act 0: none, 1: silu.
+ * out must not alias in. */
+typedef struct {
+    const float* in; long long ld; int in_off;
+    const void* w; const void* bias; int wtype;     /* w [channels][taps] */
+    float* conv_state;                              /* [n_slots][taps - 1][channels] f32 */
+    float* out; long long ld_out;
+    int channels, taps, act, residual;
+} DlConvArgs;
+int dl_causal_conv(const DlMambaBatch* batch /*host*/, int M, int n_seq, const DlConvArgs* args /*host*/, void* stream);
 typedef struct {
     const float* xbc; long long ld_xbc;      /* [M][x: heads*vdim | B: groups*state | C: groups*state] after conv + silu */
     const float* dt; long long ld_dt;        /* raw dt of head h at dt[m * ld_dt + h] */
@@ -425,6 +440,27 @@ typedef struct {
 int dl_mamba_scan_chunked_supported(int vdim, int state);
 int dl_mamba_scan_chunked(const DlMambaBatch* batch /*host*/, const DlMambaScanArgs* args /*host*/,
                           const DlMambaChunks* chunks /*host*/, void* stream);
+
+/* ---- linear attention with a fixed decay per head ("lightning", lightning.cu) ----------------------------------------
+ * Per head, state S [dim][vdim] f32 per slot:  S_t = decay_h S_(t-1) + k_t v_t^T,  y_t = S_t^T q_t.  q, k [M][heads * dim]
+ * and v [M][heads * vdim] are f32 rows (already activated); a sequence whose first row is position 0 starts from zeros. */
+typedef struct {
+    const float* q; const float* k; const float* v; long long ldq, ldk, ldv;
+    const float* decay;                      /* [heads] f32 */
+    float* y; long long ld_y;                /* [M][heads * vdim] */
+    float* state;                            /* [n_slots][heads][dim][vdim] f32 */
+    int n_heads, dim, vdim;
+} DlLightningArgs;
+int dl_lightning_scan(const DlMambaBatch* batch /*host*/, int n_seq, const DlLightningArgs* args /*host*/, void* stream);
+/* Long portions: every sequence's rows in chunks of DL_LIGHTNING_CHUNK, counted from its first row of the batch, run in
+ * parallel (three launches: the chunks' own k v^T sums, their prefix over a sequence's chunks, then the scores inside a
+ * chunk plus the carried state).  max_chunks = ceil(longest portion / DL_LIGHTNING_CHUNK); scratch:
+ * dl_lightning_chunk_floats() f32. */
+#define DL_LIGHTNING_CHUNK 64
+int dl_lightning_scan_chunked_supported(int dim, int vdim);
+long long dl_lightning_chunk_floats(int M, int n_seq, int n_heads, int dim, int vdim);
+int dl_lightning_scan_chunked(const DlMambaBatch* batch /*host*/, int n_seq, int max_chunks, const DlLightningArgs* args /*host*/,
+                              float* scratch, void* stream);
 
 /* ---- hyper-connections: `streams` copies of the residual stream per row, x[m * ldx + s * dim + i] (hyper.cu) --------
  * write (y != NULL):  x_t <- sum_s mix[s * streams + t] x_s + mult * w_out[t] * y[m]     for all t, from the old copies
@@ -455,6 +491,9 @@ typedef struct {
     const int* pos; const int* slot; const int* block_table;
     int max_pages, page_size;
     void* cache; int ctype;
+    /* separate values (v != NULL): the line is [ key[0 : dim] | value[0 : vdim] ], no rotary (rope_dims 0) */
+    const float* v; long long ldv; int vdim;
+    int qk_norm; float eps;                   /* queries and keys divided by their root mean square over dim, per head */
 } DlWindowKvArgs;
 int dl_window_kv_write(const DlWindowKvArgs* args /*host*/, int M, void* stream);
 /* out[m][h] = sum_j softmax_j(cap(scale q[m][h] . key_j)) value_j over the positions j with 0 <= pos[m] - j < window
@@ -468,6 +507,9 @@ typedef struct {
     const int* pos; const int* slot; const int* block_table;
     int max_pages, page_size;
     const void* cache; int ctype;
+    int vdim;                                 /* > 0: separate values, line [ key | value[0 : vdim] ], out [M][heads * vdim] */
+    int chunk;                                /* > 0: j is visible only inside i's chunk, floor(j / chunk) == floor(i / chunk) */
+    const float* sink;                        /* [heads] or NULL: exp(sink[h]) joins the softmax denominator, without a value */
 } DlWindowAttnArgs;
 int dl_window_attention(const DlWindowAttnArgs* args /*host*/, int M, void* stream);
 
@@ -479,6 +521,9 @@ typedef struct {
     const float* z; long long ldz;
     int M, experts, top, groups, keep, group_top, renorm;
     int* sel; float* wgt;
+    int score;                                /* 0: s = sigmoid(z); 1: s = softmax(z) over all experts */
+    float scale;                              /* 0 / 1: none; else the weights are multiplied by it (after renorm, whose
+                                                 divisor is the sum of the chosen scores + 1e-20) */
 } DlMoeSelectArgs;
 int dl_moe_select(const DlMoeSelectArgs* args /*host*/, void* stream);
 /* y[m] = sum_k wgt[m][k] * W_down[e] relu(W_up[e] x[m])^2, e = sel[m][k]; w_up [experts][ff][width], w_down
@@ -490,6 +535,9 @@ typedef struct {
     const int* sel; const float* wgt;
     float* act;
     float* y; long long ldy;
+    /* w_gate != NULL: gated experts, [experts][ff][width] like w_up:  g = min(W_gate x, limit), u = clamp(W_up x, -limit,
+     * limit), act = g * sigmoid(1.702 g) * (u + 1)  (limit <= 0: no clamps) */
+    const void* w_gate; float limit;
 } DlMoeArgs;
 int dl_moe_rows(const DlMoeArgs* args /*host*/, void* stream);
 /* Grouped form for the tensor cores.  dl_moe_plan sorts the M * top (row, expert) pairs by expert (stable) into segments
