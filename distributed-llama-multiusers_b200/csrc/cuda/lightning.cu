@@ -6,8 +6,8 @@
 // sequences with one or more consecutive rows each (DlMambaBatch); a sequence whose first row is position 0 starts from
 // zeros whatever its slot held.
 //
-// Two forms.  Token by token (decoding, short portions): one CTA per (sequence, head), the state in shared memory, the
-// rows' q and k staged a few tokens at a time.  Chunked (long portions): a sequence's rows are cut into chunks of
+// Two forms.  Token by token (decoding, short portions): one CTA per (sequence, head, slab of 64 state columns), the
+// slab in shared memory, the rows' q and k staged a few tokens at a time.  Chunked (long portions): a sequence's rows are cut into chunks of
 // LC = 64 rows, counted from the portion's first row, and unrolled as
 //     y_i = sum_{j <= i in chunk} decay^(i-j) (q_i . k_j) v_j  +  decay^(i+1) P^T q_i        i, j: offsets in the chunk
 //     P   = the state before the chunk;  state after it = decay^len P + sum_j decay^(len-1-j) k_j v_j^T
@@ -24,46 +24,58 @@ __device__ __forceinline__ float decay_pow(float log_decay, int n) { return n ==
 // ------------------------------------------------------------------------------------------------
 // token by token
 // ------------------------------------------------------------------------------------------------
-__global__ void lightning_scan_kernel(DlMambaBatch b, DlLightningArgs a) {
+// grid (sequence, head, column slab): the columns of S are independent of one another, so a CTA keeps LT_COLS of them
+// (thread = column) and every slab of a head runs in parallel
+#define LT_COLS 64
+__global__ void __launch_bounds__(LT_COLS) lightning_scan_kernel(DlMambaBatch b, DlLightningArgs a) {
     extern __shared__ float sm[];
-    const int n = blockIdx.x, h = blockIdx.y;
+    const int n = blockIdx.x, h = blockIdx.y, c = blockIdx.z * LT_COLS + threadIdx.x;
     const int D = a.dim, V = a.vdim, H = a.n_heads;
-    float* S = sm;                              // [D][V]
-    float* qs = S + (size_t)D * V;              // [LT_TB][D]
+    float* S = sm;                              // [D][LT_COLS]
+    float* qs = S + (size_t)D * LT_COLS;        // [LT_TB][D]
     float* ks = qs + LT_TB * D;                 // [LT_TB][D]
     float* Sg = a.state + ((size_t)b.seq_slot[n] * H + h) * D * V;
-    const bool fresh = b.seq_pos0[n] == 0;
-    for (int i = threadIdx.x; i < D * V; i += blockDim.x) S[i] = fresh ? 0.f : Sg[i];
+    const bool fresh = b.seq_pos0[n] == 0, live = c < V;
+    if (live)
+        for (int d = 0; d < D; ++d) S[d * LT_COLS + threadIdx.x] = fresh ? 0.f : Sg[(size_t)d * V + c];
     const float decay = a.decay[h];
     const int r0 = b.seq_start[n], r1 = b.seq_start[n + 1];
     for (int rb = r0; rb < r1; rb += LT_TB) {
         const int nt = min(LT_TB, r1 - rb);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
+        for (int i = threadIdx.x; i < nt * D; i += LT_COLS) {
             const int t = i / D, d = i - t * D;
             const int row = b.seq_rows[rb + t];
             qs[i] = a.q[(size_t)row * a.ldq + h * D + d];
             ks[i] = a.k[(size_t)row * a.ldk + h * D + d];
         }
         __syncthreads();
-        for (int c = threadIdx.x; c < V; c += blockDim.x) {
-            for (int t = 0; t < nt; ++t) {
-                const int row = b.seq_rows[rb + t];
-                const float v = a.v[(size_t)row * a.ldv + h * V + c];
-                const float* q = qs + t * D;
-                const float* k = ks + t * D;
-                float y = 0.f;
-                for (int d = 0; d < D; ++d) {
-                    const float s = fmaf(decay, S[d * V + c], k[d] * v);
-                    S[d * V + c] = s;
-                    y = fmaf(s, q[d], y);
-                }
-                a.y[(size_t)row * a.ld_y + h * V + c] = y;
+        if (!live) continue;
+        for (int t = 0; t < nt; ++t) {
+            const int row = b.seq_rows[rb + t];
+            const float v = a.v[(size_t)row * a.ldv + h * V + c];
+            const float* q = qs + t * D;
+            const float* k = ks + t * D;
+            float y0 = 0.f, y1 = 0.f;
+            int d = 0;
+            for (; d + 1 < D; d += 2) {
+                const float s0 = fmaf(decay, S[d * LT_COLS + threadIdx.x], k[d] * v);
+                const float s1 = fmaf(decay, S[(d + 1) * LT_COLS + threadIdx.x], k[d + 1] * v);
+                S[d * LT_COLS + threadIdx.x] = s0;
+                S[(d + 1) * LT_COLS + threadIdx.x] = s1;
+                y0 = fmaf(s0, q[d], y0);
+                y1 = fmaf(s1, q[d + 1], y1);
             }
+            if (d < D) {
+                const float s0 = fmaf(decay, S[d * LT_COLS + threadIdx.x], k[d] * v);
+                S[d * LT_COLS + threadIdx.x] = s0;
+                y0 = fmaf(s0, q[d], y0);
+            }
+            a.y[(size_t)row * a.ld_y + h * V + c] = y0 + y1;
         }
     }
-    __syncthreads();
-    for (int i = threadIdx.x; i < D * V; i += blockDim.x) Sg[i] = S[i];
+    if (live)
+        for (int d = 0; d < D; ++d) Sg[(size_t)d * V + c] = S[d * LT_COLS + threadIdx.x];
 }
 
 static int lightning_args_ok(const DlLightningArgs& a, const char* who) {
@@ -75,12 +87,11 @@ extern "C" int dl_lightning_scan(const DlMambaBatch* batch, int n_seq, const DlL
     const DlLightningArgs& a = *args;
     if (lightning_args_ok(a, "dl_lightning_scan")) return -1;
     if (n_seq < 1) return 0;
-    const size_t smem = ((size_t)a.dim * a.vdim + 2 * (size_t)LT_TB * a.dim) * sizeof(float);
-    if (smem > 227 * 1024) { dl_set_error("dl_lightning_scan: a %d x %d state does not fit shared memory", a.dim, a.vdim); return -1; }
+    const size_t smem = ((size_t)a.dim * LT_COLS + 2 * (size_t)LT_TB * a.dim) * sizeof(float);
+    if (smem > 227 * 1024) { dl_set_error("dl_lightning_scan: dim %d does not fit shared memory", a.dim); return -1; }
     cudaError_t e = cudaFuncSetAttribute(lightning_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { dl_set_error("dl_lightning_scan: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
-    const int threads = min(256, (a.vdim + 31) / 32 * 32);
-    lightning_scan_kernel<<<dim3(n_seq, a.n_heads), threads, smem, (cudaStream_t)stream>>>(*batch, a);
+    lightning_scan_kernel<<<dim3(n_seq, a.n_heads, (a.vdim + LT_COLS - 1) / LT_COLS), LT_COLS, smem, (cudaStream_t)stream>>>(*batch, a);
     LAYER_CHECK_LAUNCH("dl_lightning_scan");
     return 0;
 }

@@ -13,7 +13,7 @@
 #include "layer_common.cuh"
 #include "../../../include/dllama_b200.h"
 
-#define MB_MAX_TAPS 8
+#define MB_MAX_TAPS 16
 
 // input of channel ch at position q of sequence n, where the batch holds positions p0 .. p0+len-1 of the sequence
 __device__ __forceinline__ float conv_input(const DlMambaBatch& b, const float* __restrict__ in, long long ld, int in_off,
