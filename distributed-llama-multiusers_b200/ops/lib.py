@@ -166,14 +166,6 @@ def cuda_lib():
     L.dl_gemv_q40_smem_bytes.restype = i64
     L.dl_gemv_q40_smem_bytes.argtypes = [i32, i32, i32]
     L.dl_gemm_q40_tc.argtypes = [vp, i32, i32, vp, i32, i32, i32, C.POINTER(DlEpilogue), i32, vp]
-    L.dl_causal_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, C.POINTER(DlConvArgs), vp]
-    L.dl_poly_norm.argtypes = [vp, i64, vp, i64, i32, i32, vp, C.c_float, vp]
-    L.dl_lightning_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlLightningArgs), vp]
-    L.dl_lightning_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), i32, i32, C.POINTER(DlLightningArgs), vp, vp]
-    L.dl_lightning_scan_chunked_supported.argtypes = [i32, i32]
-    L.dl_lightning_scan_chunked_supported.restype = i32
-    L.dl_lightning_chunk_floats.argtypes = [i32, i32, i32, i32, i32]
-    L.dl_lightning_chunk_floats.restype = i64
     L.dl_wh_bytes.restype = i64
     L.dl_wh_bytes.argtypes = [i32, i32]
     L.dl_q40t_to_wh.argtypes = [vp, i32, i32, vp, vp]
