@@ -51,9 +51,11 @@ def parse_args():
     ap.add_argument("--layered", default="", help="instead of the headline benchmark: prefill and decode throughput of the "
                     "layer-list design (Ribivik: Mamba-2 + latent attention, bf16) beside a Q40 Llama of equal width, "
                     "feed-forward size and depth, at these sizes (comma separated: w2048, w4096); prints one JSON line")
-    ap.add_argument("--layered-design", default="ribivik", choices=("ribivik", "sunesun"),
+    ap.add_argument("--layered-design", default="ribivik", choices=("ribivik", "sunesun", "venadra"),
                     help="--layered: which layer-list design runs beside the Llama arm (ribivik: Mamba-2 + latent attention; "
-                         "sunesun: windowed attention whose values are its keys + routed experts on hyper-connected streams)")
+                         "sunesun: windowed attention whose values are its keys + routed experts on hyper-connected streams; "
+                         "venadra: lightning and chunked sink attention, PolyNorm and gated experts -- beside it also Sunesun, "
+                         "the closest layer-list design, at equal width, depth and experts)")
     ap.add_argument("--layered-layers", type=int, default=4, help="--layered: layers of both models")
     ap.add_argument("--layered-prompt", type=int, default=2048, help="--layered: prompt length (one batch)")
     return ap.parse_args()
@@ -448,6 +450,22 @@ def sunesun_config(name: str, n_layers: int, vocab: int, window: int = 1024) -> 
             "residual_mult": 0.5, "streams": 4, "layers": [dict(layer) for _ in range(n_layers)]}
 
 
+def venadra_config(name: str, n_layers: int, vocab: int, chunk: int = 1024) -> dict:
+    """Width, heads and experts of the Sunesun arm: three lightning layers to one chunked-attention layer, dense PolyNorm
+    and gated routed feed-forwards in turn (the dense one as large as the experts one token runs)."""
+    import math
+    sz, ss = LAYERED_SIZES[name], SUNESUN_SIZES[name]
+    H = sz["width"] // 128
+    light = {"heads": H, "dim": 128, "vdim": 128, "decay": [round(math.exp(-0.5 * (1.0 - h / H) ** 2 - 0.001), 6) for h in range(H)]}
+    attn = {"heads": ss["heads"], "kv_heads": ss["kv_heads"], "dim": 128, "vdim": 128, "scale": 0.125, "mask": {"size": chunk}}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": ss["expert_ff"], "limit": 7.0}, "router": {"experts": ss["experts"], "top": ss["top"], "scale": 1.0}}
+    layers = [{"type": "attention" if i % 4 == 2 else "lightning", "mixer": dict(attn if i % 4 == 2 else light),
+               "mlp": dict(moe if i % 2 else dense)} for i in range(n_layers)]
+    return {"architecture": "Venadra", "width": sz["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "canon": {"taps": 4}, "layers": layers}
+
+
 def _time_ms(fn, warmup: int, steps: int):
     import torch
     for _ in range(warmup):
@@ -515,15 +533,23 @@ def run_layered(args):
     for name in [s for s in args.layered.split(",") if s]:
         sz = LAYERED_SIZES[name]
         design = args.layered_design
-        d = os.path.join(args.model_dir, f"dllama_b200_{'layered' if design == 'ribivik' else design}_{name}_l{nl}")
-        if not os.path.exists(os.path.join(d, "model.safetensors")):
-            write_random_model(d, layered_config(sz, nl, vocab) if design == "ribivik" else sunesun_config(name, nl, vocab), seed=1)
-        eng = registry.engine_for_dir(d, max_rows=max(T, users), n_slots=users, max_seq_len=ctx, dtype="bfloat16")
-        r = _bench_engine(eng, vocab, T, users, args.warmup, args.steps)
-        r["weight_gb"] = eng.weight_bytes() / 1e9
-        eng.close()
-        del eng
-        torch.cuda.empty_cache()
+        configs = {"ribivik": lambda: layered_config(sz, nl, vocab), "sunesun": lambda: sunesun_config(name, nl, vocab),
+                   "venadra": lambda: venadra_config(name, nl, vocab)}
+
+        def layer_list_arm(dsg):
+            d = os.path.join(args.model_dir, f"dllama_b200_{'layered' if dsg == 'ribivik' else dsg}_{name}_l{nl}")
+            if not os.path.exists(os.path.join(d, "model.safetensors")):
+                write_random_model(d, configs[dsg](), seed=1)
+            eng = registry.engine_for_dir(d, max_rows=max(T, users), n_slots=users, max_seq_len=ctx, dtype="bfloat16")
+            r = _bench_engine(eng, vocab, T, users, args.warmup, args.steps)
+            r["weight_gb"] = eng.weight_bytes() / 1e9
+            eng.close()
+            del eng
+            torch.cuda.empty_cache()
+            return r
+
+        r = layer_list_arm(design)
+        beside = {"sunesun_bf16": layer_list_arm("sunesun")} if design == "venadra" else {}
         shape = dict(dim=sz["width"], hidden_dim=sz["ff"], n_layers=nl, n_heads=sz["heads"], n_kv_heads=8, vocab_size=vocab,
                      max_seq_len=8192, rope_theta=10000, rope=None)
         path = os.path.join(args.model_dir, f"dllama_b200_llama_{name}_l{nl}_q40.m")
@@ -535,7 +561,7 @@ def run_layered(args):
         le.close()
         del le
         torch.cuda.empty_cache()
-        rows[name] = {f"{args.layered_design}_bf16": r, "llama_q40": q}
+        rows[name] = {f"{args.layered_design}_bf16": r, **beside, "llama_q40": q}
     print(json.dumps({"layered": rows, "design": args.layered_design, "layers": nl, "prompt": T, "users": users, "steps": args.steps, "warmup": args.warmup,
                       "data": "synthetic", "clocks": sampler.stop()}), flush=True)
 
