@@ -83,15 +83,84 @@ static int lightning_args_ok(const DlLightningArgs& a, const char* who) {
     return 0;
 }
 
+// The same with the state in registers, for dim <= 4 * NR: a CTA owns LR_COLS columns of one head's S; thread (column, dq)
+// keeps rows dq, dq + 4, ... of its column (NR registers), the four threads of a column are neighbouring lanes and sum
+// their shares of y by two shuffles.  Many small CTAs: a decode step of one sequence still fills heads * vdim / 32 of them.
+#define LR_COLS 32
+template <int NR>
+__global__ void __launch_bounds__(LR_COLS * 4) lightning_scan_reg_kernel(DlMambaBatch b, DlLightningArgs a) {
+    extern __shared__ float sm[];
+    const int n = blockIdx.x, h = blockIdx.y, dq = threadIdx.x & 3, c = blockIdx.z * LR_COLS + (threadIdx.x >> 2);
+    const int D = a.dim, V = a.vdim, H = a.n_heads;
+    float* qs = sm;                             // [LT_TB][D]
+    float* ks = qs + LT_TB * D;                 // [LT_TB][D]
+    float* Sg = a.state + ((size_t)b.seq_slot[n] * H + h) * D * V;
+    const bool fresh = b.seq_pos0[n] == 0, live = c < V;
+    float s[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int d = i * 4 + dq;
+        s[i] = (live && !fresh && d < D) ? Sg[(size_t)d * V + c] : 0.f;
+    }
+    const float decay = a.decay[h];
+    const int r0 = b.seq_start[n], r1 = b.seq_start[n + 1];
+    for (int rb = r0; rb < r1; rb += LT_TB) {
+        const int nt = min(LT_TB, r1 - rb);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * D; i += LR_COLS * 4) {
+            const int t = i / D, d = i - t * D;
+            const int row = b.seq_rows[rb + t];
+            qs[i] = a.q[(size_t)row * a.ldq + h * D + d];
+            ks[i] = a.k[(size_t)row * a.ldk + h * D + d];
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const int row = b.seq_rows[rb + t];
+            const float v = live ? a.v[(size_t)row * a.ldv + h * V + c] : 0.f;
+            const float* q = qs + t * D;
+            const float* k = ks + t * D;
+            float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < NR; i += 2) {
+                const int d = i * 4 + dq;
+                if (d < D) { s[i] = fmaf(decay, s[i], k[d] * v); y0 = fmaf(s[i], q[d], y0); }
+                if (d + 4 < D) { s[i + 1] = fmaf(decay, s[i + 1], k[d + 4] * v); y1 = fmaf(s[i + 1], q[d + 4], y1); }
+            }
+            float y = y0 + y1;
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            if (live && dq == 0) a.y[(size_t)row * a.ld_y + h * V + c] = y;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int d = i * 4 + dq;
+            if (d < D) Sg[(size_t)d * V + c] = s[i];
+        }
+    }
+}
+
 extern "C" int dl_lightning_scan(const DlMambaBatch* batch, int n_seq, const DlLightningArgs* args, void* stream) {
     const DlLightningArgs& a = *args;
     if (lightning_args_ok(a, "dl_lightning_scan")) return -1;
     if (n_seq < 1) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a.dim <= 256) {                        // the state in registers
+        const size_t smem = 2 * (size_t)LT_TB * a.dim * sizeof(float);
+        dim3 grid(n_seq, a.n_heads, (a.vdim + LR_COLS - 1) / LR_COLS);
+        if (a.dim <= 32) lightning_scan_reg_kernel<8><<<grid, LR_COLS * 4, smem, st>>>(*batch, a);
+        else if (a.dim <= 64) lightning_scan_reg_kernel<16><<<grid, LR_COLS * 4, smem, st>>>(*batch, a);
+        else if (a.dim <= 128) lightning_scan_reg_kernel<32><<<grid, LR_COLS * 4, smem, st>>>(*batch, a);
+        else lightning_scan_reg_kernel<64><<<grid, LR_COLS * 4, smem, st>>>(*batch, a);
+        LAYER_CHECK_LAUNCH("dl_lightning_scan");
+        return 0;
+    }
     const size_t smem = ((size_t)a.dim * LT_COLS + 2 * (size_t)LT_TB * a.dim) * sizeof(float);
     if (smem > 227 * 1024) { dl_set_error("dl_lightning_scan: dim %d does not fit shared memory", a.dim); return -1; }
     cudaError_t e = cudaFuncSetAttribute(lightning_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { dl_set_error("dl_lightning_scan: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
-    lightning_scan_kernel<<<dim3(n_seq, a.n_heads, (a.vdim + LT_COLS - 1) / LT_COLS), LT_COLS, smem, (cudaStream_t)stream>>>(*batch, a);
+    lightning_scan_kernel<<<dim3(n_seq, a.n_heads, (a.vdim + LT_COLS - 1) / LT_COLS), LT_COLS, smem, st>>>(*batch, a);
     LAYER_CHECK_LAUNCH("dl_lightning_scan");
     return 0;
 }
@@ -174,11 +243,21 @@ __global__ void __launch_bounds__(256) lightning_chunk_prefix_kernel(DlMambaBatc
     const float logd = logf(a.decay[h]);
     float R = b.seq_pos0[n] == 0 ? 0.f : *Sg;
     const int nc = (total + LC - 1) / LC;
-    for (int c = 0; c < nc; ++c) {
-        float* p = scratch + ((size_t)(s0 / LC + n + c) * H + h) * D * V + e;
-        const float own = *p;
-        *p = R;
-        R = fmaf(decay_pow(logd, min(LC, total - c * LC)), R, own);
+    const float full = decay_pow(logd, LC);
+    float* p0 = scratch + ((size_t)(s0 / LC + n) * H + h) * D * V + e;
+    const size_t step = (size_t)H * D * V;
+    for (int c0 = 0; c0 < nc; c0 += 8) {          // eight chunks' sums are loaded together, then chained
+        float own[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) own[i] = c0 + i < nc ? p0[(size_t)(c0 + i) * step] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i;
+            if (c < nc) {
+                p0[(size_t)c * step] = R;
+                R = fmaf(c == nc - 1 ? decay_pow(logd, total - c * LC) : full, R, own[i]);
+            }
+        }
     }
     *Sg = R;
 }
@@ -192,7 +271,7 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_out_kernel(DlMamba
     const int D = a.dim, V = a.vdim, H = a.n_heads, DP = D + 1;
     float* qs = sm;                             // [LC][D + 1]
     float* ks = qs + (size_t)LC * DP;           // [LC][D + 1]
-    float* vs = ks + (size_t)LC * DP;           // [LC][V]
+    float* vs = ks + (size_t)LC * max(DP, 128); // [LC][V]
     float* A = vs + (size_t)LC * V;             // [LC][LC + 1]
     const float logd = logf(a.decay[h]);
     for (int i = threadIdx.x; i < LC * D; i += LC_THREADS) {
@@ -241,10 +320,12 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_out_kernel(DlMamba
     }
     __syncthreads();
     const float* P = scratch + ((size_t)ci * H + h) * D * V;
+    float* Ps = ks;                             // [LC][128]: LC rows of the carried state, in the keys' place
     float carry[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) carry[r] = decay_pow(logd, tb * 4 + r + 1);
     for (int c0 = 0; c0 < V; c0 += 128) {
+        const int cw = min(128, V - c0);
         float acc[4][8], pacc[4][8];
 #pragma unroll
         for (int r = 0; r < 4; ++r)
@@ -262,17 +343,26 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_out_kernel(DlMamba
 #pragma unroll
                 for (int u = 0; u < 8; ++u) acc[r][u] = fmaf(av[r], vv[u], acc[r][u]);
         }
-        if (tb * 4 < len) {
-            for (int d = 0; d < D; ++d) {
-                float qv[4], pv[8];
+        for (int d0 = 0; d0 < D; d0 += LC) {        // LC rows of P at a time
+            const int dn = min(LC, D - d0);
+            __syncthreads();                        // the scores (first pass) or the previous rows are done with
+            for (int i = threadIdx.x; i < dn * 128; i += LC_THREADS) {
+                const int d = i >> 7, cc = i & 127;
+                Ps[i] = cc < cw ? P[(size_t)(d0 + d) * V + c0 + cc] : 0.f;
+            }
+            __syncthreads();
+            if (tb * 4 < len) {
+                for (int d = 0; d < dn; ++d) {
+                    float qv[4], pv[8];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) qv[r] = qs[(tb * 4 + r) * DP + d];
+                    for (int r = 0; r < 4; ++r) qv[r] = qs[(tb * 4 + r) * DP + d0 + d];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { const int cc = c0 + cb + 16 * u; pv[u] = cc < V ? P[(size_t)d * V + cc] : 0.f; }
+                    for (int u = 0; u < 8; ++u) pv[u] = Ps[d * 128 + cb + 16 * u];
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
+                    for (int r = 0; r < 4; ++r)
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) pacc[r][u] = fmaf(qv[r], pv[u], pacc[r][u]);
+                        for (int u = 0; u < 8; ++u) pacc[r][u] = fmaf(qv[r], pv[u], pacc[r][u]);
+                }
             }
         }
 #pragma unroll
@@ -289,8 +379,9 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_out_kernel(DlMamba
     }
 }
 
-static size_t lightning_out_smem(int dim, int vdim) {
-    return ((size_t)2 * LC * (dim + 1) + (size_t)LC * vdim + (size_t)LC * (LC + 1)) * sizeof(float);
+static size_t lightning_out_smem(int dim, int vdim) {      // the keys' region later holds LC x 128 values of the carried state
+    const size_t keys = (size_t)LC * (dim + 1) > (size_t)LC * 128 ? (size_t)LC * (dim + 1) : (size_t)LC * 128;
+    return ((size_t)LC * (dim + 1) + keys + (size_t)LC * vdim + (size_t)LC * (LC + 1)) * sizeof(float);
 }
 
 // 0 if the chunked kernels take these sizes

@@ -9,6 +9,10 @@
       the windowed-attention tile kernel alone (2048 rows of one sequence, 16 / 8 heads of 128, 64 rotated dims, window
       1024, soft cap 50), timed with CUDA events; small enough for a full counter capture:
         ncu --set full --clock-control none -k regex:window_attention_mma -s 1 -c 2 -o out python scripts/profile_layered.py window-attention
+  python scripts/profile_layered.py lightning-scan
+      the chunk-parallel linear-attention scan alone (2048 rows of one sequence, 16 heads of 128 x 128), timed with CUDA
+      events, then the token-by-token kernel on 32 sequences of one row:
+        ncu --set full --clock-control none -k regex:lightning_chunk_out -s 1 -c 2 -o out python scripts/profile_layered.py lightning-scan
 Run the plain command first; capture only if it exits 0.
 """
 import argparse
@@ -77,13 +81,45 @@ def window_attention(a):
     print("GFLOP over the visible keys: %.2f" % (keys * H * d * 4 / 1e9))
 
 
+def lightning_scan(a):
+    import torch
+    from dllama_b200.ops import layers as L
+    H, d, dv, n, users = 16, 128, 128, 2048, 32
+    g = torch.Generator().manual_seed(1)
+    qkv = (torch.randn(n, H * (2 * d + dv), generator=g) * 0.3).cuda()
+    decay = torch.linspace(0.6, 0.999, H).cuda()
+    y = torch.zeros(n, H * dv, device="cuda")
+    state = torch.zeros(users, H, d, dv, device="cuda")
+    scratch = torch.zeros(L.lightning_chunk_floats(n, 1, H, d, dv), device="cuda")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    keep = [i32(list(range(n))), i32([0] * n), i32([0, n]), i32(list(range(n))), i32([0]), i32([0])]
+    b = L.mamba_batch(*keep)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(4):
+        ev0.record()
+        L.lightning_scan(b, 1, qkv, qkv[:, H * d:], qkv[:, 2 * H * d:], decay, y, state, H, d, dv, max_chunks=n // L.LIGHTNING_CHUNK, scratch=scratch)
+        ev1.record()
+        torch.cuda.synchronize()
+        print("chunked scan, %d rows: %.1f us" % (n, ev0.elapsed_time(ev1) * 1e3))
+    print("GFLOP (state update and read-out, 4 dim vdim per row and head): %.2f" % (n * H * 4 * d * dv / 1e9))
+    keep2 = [i32([5] * users), i32(list(range(users))), i32(list(range(users + 1))), i32(list(range(users))), i32(list(range(users))), i32([5] * users)]
+    b2 = L.mamba_batch(*keep2)
+    for m in (1, users):
+        for _ in range(3):
+            ev0.record()
+            L.lightning_scan(b2, m, qkv, qkv[:, H * d:], qkv[:, 2 * H * d:], decay, y, state, H, d, dv)
+            ev1.record()
+            torch.cuda.synchronize()
+            print("token-by-token scan, %d sequences of one row: %.1f us for %.1f MB of state read and written" % (m, ev0.elapsed_time(ev1) * 1e3, 2 * m * H * d * dv * 4 / 1e6))
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=("steps", "window-attention"))
+    ap.add_argument("what", choices=("steps", "window-attention", "lightning-scan"))
     ap.add_argument("--design", default="sunesun", choices=("ribivik", "sunesun", "venadra"))
     ap.add_argument("--size", default="w2048")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--model-dir", default="/tmp")
     a = ap.parse_args()
-    steps(a) if a.what == "steps" else window_attention(a)
+    {"steps": steps, "window-attention": window_attention, "lightning-scan": lightning_scan}[a.what](a)
