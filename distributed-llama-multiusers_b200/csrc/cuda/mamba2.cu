@@ -29,18 +29,28 @@ __device__ __forceinline__ float conv_input(const DlMambaBatch& b, const float* 
     return conv_state[((size_t)b.seq_slot[n] * (taps - 1) + k) * channels + ch];
 }
 
-// out[row][ch] = act(bias[ch] + sum_k w[ch][k] * input(pos - (taps-1) + k)) (+ input(pos) if residual)
+// out[row][ch] = act(bias[ch] + sum_k w[ch][k] * input(pos - (taps-1) + k)) (+ input(pos) if residual).  Where each tap's
+// inputs lie (a row of the batch, a carried row of the slot, or nothing before the sequence's start) is the same for all
+// channels of a row: found once per CTA, then every channel reads through the taps' pointers.
 template <typename WT>
 __global__ void __launch_bounds__(256) mamba_conv_kernel(DlMambaBatch b, const float* __restrict__ in, long long ld, int in_off,
                                                          const WT* __restrict__ w, const WT* __restrict__ bias,
                                                          const float* __restrict__ conv_state, float* __restrict__ out, long long ld_out,
                                                          int channels, int taps, int act, int residual) {
+    __shared__ const float* src[MB_MAX_TAPS];
     const int m = blockIdx.x;
-    const int n = b.row_seq[m], pos = b.pos[m];
+    if (threadIdx.x < taps) {
+        const int n = b.row_seq[m], q = b.pos[m] - (taps - 1) + threadIdx.x, p0 = b.seq_pos0[n];
+        const float* p = nullptr;
+        if (q >= p0) p = in + (size_t)b.seq_rows[b.seq_start[n] + (q - p0)] * ld + in_off;
+        else if (q >= 0) p = conv_state + ((size_t)b.seq_slot[n] * (taps - 1) + (q - p0 + (taps - 1))) * channels;
+        src[threadIdx.x] = p;
+    }
+    __syncthreads();
     for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
         float acc = bias ? ld_f(bias + ch) : 0.f;
         for (int k = 0; k < taps; ++k)
-            acc = fmaf(ld_f(w + (size_t)ch * taps + k), conv_input(b, in, ld, in_off, conv_state, channels, taps, n, pos - (taps - 1) + k, ch), acc);
+            if (src[k]) acc = fmaf(ld_f(w + (size_t)ch * taps + k), src[k][ch], acc);
         if (act) acc = silu_f(acc);
         if (residual) acc += in[(size_t)m * ld + in_off + ch];
         out[(size_t)m * ld_out + ch] = acc;
