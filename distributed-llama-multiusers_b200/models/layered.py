@@ -450,7 +450,7 @@ class LightningMixer:
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str, share: Optional["LightningMixer"] = None):
         self.eng, self.index = eng, index
         self.H, self.dim, self.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
-        decay = [float(x) for x in m["decay"]]
+        decay = [float(x) for x in m["decay"]] if isinstance(m["decay"], (list, tuple)) else [float(m["decay"])] * self.H
         if len(decay) != self.H or not all(0.0 <= x <= 1.0 for x in decay):
             raise ValueError(f"layer {index}: decay must give one number in [0, 1] per head")
         self.decay = torch.tensor(decay, dtype=torch.float32, device=eng.device)

@@ -101,3 +101,56 @@ def test_sunesun_oracle_window_and_prefix_property():
     c = S.model_logits(t, cfg, other)
     # two layers of window 6 reach 10 positions back: position 3 is seen up to position 13 and by nothing after it
     assert not torch.allclose(a[13], c[13], atol=1e-9) and torch.allclose(a[14:], c[14:], atol=1e-9)
+
+
+# ---- Venadra: configuration, design traits, weight names, the oracle's own chunks and recurrence ----------------------------
+def test_venadra_configuration_traits_and_tensor_names(tmp_path):
+    from dllama_b200.models.layered import DESIGNS, example_config_venadra
+    cfg = example_config_venadra()
+    d = str(tmp_path / "v")
+    tensors = write_random_model(d, cfg, seed=1)
+    assert registry.architecture_of(d) == "Venadra" and "Venadra" in registry.ARCHITECTURES
+    c = LayerListConfig.load(d)
+    assert (c.residual, c.streams, c.hyper_weights, c.canon_taps, c.embed_scale) == ("hyper", 1, False, 3, 4.0)
+    assert c.traits is DESIGNS["Venadra"] and c.traits["attention"]["mask"] == "chunk" and c.traits["moe"]["score"] == "softmax"
+    assert [l.weights_of for l in c.layers] == [None, None, None, 0, 1]
+    assert tensors["l0.norm1"].dim() == 0 and tensors["final.norm"].dim() == 0 and tensors["l0.canon1"].shape == (160, 3)
+    assert tensors["l0.mix.norm"].shape == (3 * 24,) and tensors["l0.mlp.act"].shape == (4,) and tensors["l1.mix.sink"].shape == (6,)
+    assert tensors["l1.mix.v"].shape == (3 * 32, 160) and tensors["l1.mlp.e5.gate"].shape == (48, 160)
+    assert "l3.mix.q" not in tensors and "l4.canon1" not in tensors and "l0.hc1.in" not in tensors
+    # the same mixer types under another design keep that design's meaning: no sink, gate or value projection for Sunesun
+    from dllama_b200.models.layered import example_config_sunesun
+    assert "l0.mix.sink" not in random_tensors(example_config_sunesun(), seed=1)
+    bad = json.loads(json.dumps(cfg))
+    bad["layers"][3]["weights_of"] = 4                      # a layer that has no weights of its own
+    with pytest.raises(ValueError):
+        LayerListConfig.from_dict(bad)
+
+
+def test_venadra_oracle_chunks_recurrence_and_prefix_property():
+    """The oracle itself: appended tokens change nothing before them; through chunked attention and the short convolution
+    alone a changed token reaches one chunk further per layer and no more; a lightning layer carries it to the end; the
+    recurrence equals its unrolled sum."""
+    import venadra_oracle as V
+    attn = {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 12, "scale": 0.3, "mask": {"size": 6}}
+    cfg = {"architecture": "Venadra", "width": 48, "vocab": 40, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0}, "canon": {"taps": 2},
+           "layers": [{"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": 32}},
+                      {"type": "attention", "mixer": attn, "mlp": None, "weights_of": 0}]}
+    cfg["layers"][1]["mlp"] = cfg["layers"][0]["mlp"]
+    t = random_tensors(cfg, seed=2)
+    toks = torch.randint(0, 40, (30,), generator=torch.Generator().manual_seed(3)).tolist()
+    a, b = V.model_logits(t, cfg, toks), V.model_logits(t, cfg, toks[:11])
+    assert torch.allclose(a[:11], b, atol=1e-9)
+    other = list(toks)
+    other[3] = (toks[3] + 1) % 40
+    c = V.model_logits(t, cfg, other)
+    # layer 0: positions 3..5 (its chunk) and, by the convolution of layer 1, position 6, which layer 1 spreads over chunk 6..11
+    assert torch.allclose(a[:3], c[:3], atol=1e-9) and not torch.allclose(a[11], c[11], atol=1e-9) and torch.allclose(a[12:], c[12:], atol=1e-9)
+    cfg["layers"][1] = {"type": "lightning", "mixer": {"heads": 2, "dim": 4, "vdim": 6, "decay": [0.99, 0.5]}, "mlp": None}
+    t = random_tensors(cfg, seed=2)
+    assert not torch.allclose(V.model_logits(t, cfg, toks)[-1], V.model_logits(t, cfg, other)[-1], atol=1e-9)
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(9, n, generator=g, dtype=torch.float64) for n in (4, 4, 6))
+    o = V.decayed_linear_attention(q, k, v, 0.8)
+    want = sum(0.8 ** (8 - j) * float(q[8] @ k[j]) * v[j] for j in range(9))
+    assert torch.allclose(o[8], want, atol=1e-12)
