@@ -456,8 +456,8 @@ def venadra_config(name: str, n_layers: int, vocab: int, chunk: int = 1024) -> d
     import math
     sz, ss = LAYERED_SIZES[name], SUNESUN_SIZES[name]
     H = sz["width"] // 128
-    light = {"heads": H, "dim": 128, "vdim": 128, "decay": [round(math.exp(-0.5 * (1.0 - h / H) ** 2 - 0.001), 6) for h in range(H)]}
-    attn = {"heads": ss["heads"], "kv_heads": ss["kv_heads"], "dim": 128, "vdim": 128, "scale": 0.125, "mask": {"size": chunk}}
+    light = {"heads": H, "dim": 128, "vdim": 128, "decay": [round(0.999 - 0.45 * (1.0 - h / H) ** 2, 6) for h in range(H)]}
+    attn = {"heads": ss["heads"], "kv_heads": ss["kv_heads"], "dim": 128, "vdim": 128, "scale": 0.1, "mask": {"size": chunk}}
     dense = {"kind": "dense", "ff": sz["ff"]}
     moe = {"kind": "moe", "expert": {"ff": ss["expert_ff"], "limit": 7.0}, "router": {"experts": ss["experts"], "top": ss["top"], "scale": 1.0}}
     layers = [{"type": "attention" if i % 4 == 2 else "lightning", "mixer": dict(attn if i % 4 == 2 else light),

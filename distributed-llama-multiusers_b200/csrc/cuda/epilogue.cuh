@@ -177,7 +177,7 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
         // dense-weight models: an element-wise op on the f32 result, then a plain store (one destination)
         if (e.dense_op == DL_DENSE_GLU_CLAMP) {
             // output rows interleaved (gate_j, up_j): thread j < rows/2 owns value j of the tile and stores column
-            // grow0 / 2 + j:  g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+            // grow0 / 2 + j:  a = min(gate, limit), b = clamp(up, +-limit), hidden = a * sigma(1.702 a) * (1 + b)
             const int col = (grow0 >> 1) + tid;
             if (tid < (rows >> 1) && 2 * col + 1 < d_real) {
                 const size_t ld = (size_t)e.ld;

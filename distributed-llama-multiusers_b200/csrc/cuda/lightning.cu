@@ -1,7 +1,7 @@
 // Linear attention with a fixed decay per head ("lightning" attention).  Per head, with q_t, k_t in R^dim and v_t in
 // R^vdim (already activated) and a constant 0 <= decay_h <= 1:
-//     S_t = decay_h S_(t-1) + k_t v_t^T          S: [dim][vdim], f32, one per sequence slot and head
-//     y_t = S_t^T q_t
+//     S <- lambda S + k (x) v     (outer product)      S: [dim][vdim], f32, one per sequence slot and head, lambda = decay_h
+//     y  = S^T q                  (with the S just updated)
 // Everything here is f32: the state, the scores inside a chunk, the powers of the decay.  A batch is any mix of
 // sequences with one or more consecutive rows each (DlMambaBatch); a sequence whose first row is position 0 starts from
 // zeros whatever its slot held.

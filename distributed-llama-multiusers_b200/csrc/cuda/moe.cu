@@ -1,6 +1,6 @@
 // Routed experts: every token runs `top` of `experts` small feed-forward layers  W_down act(W_up h),  act = relu(.)^2,
 // and sums their outputs weighted by the router's scores.  Gated experts (a third matrix W_gate per expert) use
-// act = g * sigmoid(1.702 g) * (u + 1) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit) instead.
+// hidden = a sigma(1.702 a) (1 + b) with a = min(gate . h, limit), b = clamp(up . h, +-limit) instead (sigma: logistic).
 //
 // Routing (dl_moe_select), from the router logits z[M][experts] (a dense product, f32):  s = sigmoid(z), or s =
 // softmax(z) over all experts (`score` 1); the chosen weights may be multiplied by a constant (`scale`).  The experts
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_up_rows_kernel(DlMoeArgs a,
     const int m = pair / a.top, e = a.sel[pair];
     const WT* w = (const WT*)a.w_up + ((size_t)e * a.ff + f) * a.width;
     const float v = warp_dot<WT, RX>(w, a.x + (size_t)m * a.ldx, a.width, vec, lane);
-    if (a.w_gate != nullptr) {                // gated: g * sigmoid(1.702 g) * (u + 1) on the clamped products
+    if (a.w_gate != nullptr) {                // gated: a sigma(1.702 a) (1 + b) on the clamped products
         const WT* wg = (const WT*)a.w_gate + ((size_t)e * a.ff + f) * a.width;
         float g = warp_dot<WT, RX>(wg, a.x + (size_t)m * a.ldx, a.width, vec, lane), u = v;
         if (a.limit > 0.f) { g = fminf(g, a.limit); u = fminf(fmaxf(u, -a.limit), a.limit); }

@@ -13,9 +13,9 @@
 //
 // The same kernels serve attention with values of their own (vdim > 0): the line is [ key[0 : dim] | value[0 : vdim] ],
 // written by attn_kv_write_kernel, which can divide every query and key head by its root mean square first.  Two more
-// options of the score side: a chunked mask (chunk > 0: j is visible to i only if floor(j / chunk) == floor(i / chunk),
-// chunks counted from position 0 of the sequence) and a sink per head (exp(sink_h) joins the softmax denominator,
-// with no key and no value).
+// options of the score side: a chunked mask (chunk > 0: j is visible to i only if floor(j / chunk) == floor(i / chunk);
+// the borders are multiples of `chunk` in sequence positions, wherever a portion starts) and a sink per head: the softmax
+// denominator gets one more term exp(sink_h) that pulls weight away from the keys and contributes no value.
 //
 // Kernels: the cache writer, which also turns the queries in place (one launch, cos and sin formed once per row and
 // pair); the per-row attention kernel (exact f32 arithmetic on either cache type; one CTA per

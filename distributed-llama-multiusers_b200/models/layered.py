@@ -302,7 +302,8 @@ class Mamba2Mixer:
 
 class DenseFeedForward:
     """Tensors <prefix>up, down:  W_down act(W_up h).  act = relu(.)^2, or (design trait dense_act "polynorm", tensor
-    <prefix>act = [a, b, c, e]) PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e with N the RMS normalisation of a row."""
+    <prefix>act = [c1, c2, c3, c0]) PolyNorm: c0 + sum_p cp z^p / rms(z^p), p = 1..3, with the powers taken element-wise and
+    the root mean square (eps inside) over a row."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng = eng
@@ -337,7 +338,7 @@ class WindowAttentionMixer:
              holds the rotated key followed by the unrotated head of k;
       values "own": a projection <prefix>v of vdim numbers per key/value head, the line holds key + value (no rotary);
       mask "window" (default): a position sees itself and the mask.size - 1 before it (absent: everything before it);
-      mask "chunk": position i sees j <= i with floor(j / size) = floor(i / size), chunks counted from position 0;
+      mask "chunk": position i sees j <= i with floor(j / size) = floor(i / size): chunk borders are multiples of size in sequence positions;
       qk_norm: every query and key head is divided by its root mean square (eps of the model) before the scores;
       sink: <prefix>sink [heads], exp(sink_h) joins the softmax denominator without a key or a value;
       gate: <prefix>g, the concatenated heads are multiplied by sigmoid(W_g h) before the output projection."""
@@ -443,8 +444,8 @@ class WindowAttentionMixer:
 
 class LightningMixer:
     """Linear attention with a fixed decay per head.  Tensors <prefix>q, k, v, g, o, norm.  Sizes: heads, dim, vdim,
-    decay [heads].  q = silu(W_q h), k = silu(W_k h), v = silu(W_v h); per head S <- decay_h S + k v^T (f32, one state
-    [dim][vdim] per slot and head), o = S^T q; the concatenated heads are RMS-normed together (weight `norm`), multiplied
+    decay [heads].  q, k, v = SiLU of their projections of h; per head S <- lambda S + k (x) v with lambda = decay_h (f32, one state
+    [dim][vdim] per slot and head), o = S^T q; all heads' outputs side by side get ONE RMS norm (weight `norm` [heads * vdim]), are multiplied
     by sigmoid(W_g h) and projected by W_o."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str, share: Optional["LightningMixer"] = None):
@@ -498,7 +499,7 @@ class RoutedExperts:
       score "sigmoid" (default): scores sigmoid(z); experts form `count` groups of neighbours scored by the sum of their
             two largest scores, only the `keep` best groups are eligible;  "softmax": scores softmax(z) over all experts;
       renorm: the chosen scores are divided by their sum (+ 1e-20); router.scale then multiplies the weights;
-      gated:  an expert is W_down (g sigmoid(1.702 g) (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit);
+      gated:  an expert is W_down (a sigma(1.702 a) (1 + b)), a = min(gate . h, limit), b = clamp(up . h, +-limit);
               otherwise W_down relu(W_up h)^2.
     The `top` best eligible experts run and their outputs are summed with the weights."""
 

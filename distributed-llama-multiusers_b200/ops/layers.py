@@ -396,7 +396,7 @@ def moe_select(z: torch.Tensor, M: int, experts: int, top: int, groups: int, kee
 def moe_rows(w_up: torch.Tensor, w_down: torch.Tensor, x: torch.Tensor, M: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
              act: torch.Tensor, y: torch.Tensor, round_x: bool, w_gate: Optional[torch.Tensor] = None, limit: float = 0.0):
     """w_up [experts][ff][width], w_down [experts][width][ff]; one product per (row, chosen expert) pair.  With w_gate
-    (like w_up) the experts are gated: g sigmoid(1.702 g) (u + 1) on the products clamped by `limit`, else relu(u)^2."""
+    (like w_up) the experts are gated: a sigma(1.702 a) (1 + b) on the products a, b clamped by `limit`, else relu(u)^2."""
     a = DlMoeArgs()
     a.w_up, a.w_down, a.wtype = w_up.data_ptr(), w_down.data_ptr(), _type(w_up)
     a.width, a.ff, a.top, a.M, a.round_x = w_up.shape[2], w_up.shape[1], top, M, 1 if round_x else 0

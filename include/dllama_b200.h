@@ -442,7 +442,7 @@ int dl_mamba_scan_chunked(const DlMambaBatch* batch /*host*/, const DlMambaScanA
                           const DlMambaChunks* chunks /*host*/, void* stream);
 
 /* ---- linear attention with a fixed decay per head ("lightning", lightning.cu) ----------------------------------------
- * Per head, state S [dim][vdim] f32 per slot:  S_t = decay_h S_(t-1) + k_t v_t^T,  y_t = S_t^T q_t.  q, k [M][heads * dim]
+ * Per head, state S [dim][vdim] f32 per slot:  S <- lambda S + k (x) v (lambda = decay[h]), then y = S^T q.  q, k [M][heads * dim]
  * and v [M][heads * vdim] are f32 rows (already activated); a sequence whose first row is position 0 starts from zeros. */
 typedef struct {
     const float* q; const float* k; const float* v; long long ldq, ldk, ldv;
@@ -493,7 +493,7 @@ typedef struct {
     void* cache; int ctype;
     /* separate values (v != NULL): the line is [ key[0 : dim] | value[0 : vdim] ], no rotary (rope_dims 0) */
     const float* v; long long ldv; int vdim;
-    int qk_norm; float eps;                   /* queries and keys divided by their root mean square over dim, per head */
+    int qk_norm; float eps;                   /* every query and key head h becomes h / sqrt(mean(h^2) + eps) */
 } DlWindowKvArgs;
 int dl_window_kv_write(const DlWindowKvArgs* args /*host*/, int M, void* stream);
 /* out[m][h] = sum_j softmax_j(cap(scale q[m][h] . key_j)) value_j over the positions j with 0 <= pos[m] - j < window
@@ -535,8 +535,8 @@ typedef struct {
     const int* sel; const float* wgt;
     float* act;
     float* y; long long ldy;
-    /* w_gate != NULL: gated experts, [experts][ff][width] like w_up:  g = min(W_gate x, limit), u = clamp(W_up x, -limit,
-     * limit), act = g * sigmoid(1.702 g) * (u + 1)  (limit <= 0: no clamps) */
+    /* w_gate != NULL: gated experts, [experts][ff][width] like w_up:  a = min(gate . x, limit), b = clamp(up . x, +-limit),
+     * hidden = a * sigma(1.702 a) * (1 + b)  (limit <= 0: no clamps) */
     const void* w_gate; float limit;
 } DlMoeArgs;
 int dl_moe_rows(const DlMoeArgs* args /*host*/, void* stream);

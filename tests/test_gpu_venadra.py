@@ -267,7 +267,7 @@ def _standout_case(block, T, H, G, d, dv, seed):
 
 
 @pytest.mark.parametrize("ctype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("block,H,G,d,dv", [(37, 6, 3, 24, 40), (32, 2, 2, 16, 16), (5, 4, 1, 32, 8), (0, 3, 1, 20, 20), (96, 10, 1, 16, 24)])
+@pytest.mark.parametrize("block,H,G,d,dv", [(37, 6, 3, 24, 40), (32, 2, 2, 16, 16), (5, 4, 1, 32, 8), (0, 3, 1, 20, 20), (90, 10, 1, 16, 24)])
 def test_chunked_attention_sees_exactly_its_chunk(ctype, block, H, G, d, dv):
     T = 150
     q, k, v = _standout_case(block or 50, T, H, G, d, dv, seed=block + H)
@@ -538,12 +538,12 @@ def _random_config(rng):
         if rng.random() < 0.5:
             H = rng.choice([1, 2, 3, 5])
             kind, m = "lightning", _light(heads=H, dim=rng.choice([8, 16, 24, 48, 64, 100]), vdim=rng.choice([8, 16, 40, 64, 72, 128]),
-                                           decay=[rng.choice([1.0, 0.999, 0.97, 0.8, 0.3, 0.6065]) for _ in range(H)])
+                                           decay=[rng.choice([1.0, 0.9995, 0.97, 0.8, 0.3, 0.55]) for _ in range(H)])
         else:
             G, rep = rng.choice([1, 2, 3, 4]), rng.choice([1, 2, 3, 5, 8])
             dim = rng.choice([16, 24, 48, 64, 80, 96, 128])
             kind, m = "attention", _attn(heads=G * rep, kv_heads=G, dim=dim, vdim=rng.choice([dim, dim, 8, 40, 72]),
-                                           size=rng.choice([0, 1, 2, 7, 31, 32, 33, 65, 100]), scale=rng.choice([0.05, 0.125, 0.4]))
+                                           size=rng.choice([0, 1, 2, 7, 31, 32, 33, 65, 100]), scale=rng.choice([0.05, 0.15, 0.4]))
         mlp = None
         r = rng.random()
         if r < 0.45:
