@@ -169,7 +169,7 @@ DL_DEVINL void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" :
 DL_DEVINL void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // --------------------------------------------------------------------------------------------
-// bulk async copy global -> shared (1-D TMA; SASS: UBLKCP), completion on an mbarrier
+// bulk async copy global -> shared (1-D TMA), completion on an mbarrier
 // --------------------------------------------------------------------------------------------
 DL_DEVINL void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
     asm volatile(

@@ -2,7 +2,7 @@
 //
 // Design (B200-first, not a port of matmul_Q80_Q40_F32, src/nn/nn-cpu-ops.cpp:222-440):
 //  * weights live in HBM as Q40T tiles (common.cuh): each pipeline stage is a contiguous bulk
-//    async copy (cp.async.bulk -> SASS UBLKCP) of a 128x128 tile into shared memory, completion
+//    async copy (cp.async.bulk) of a 128x128 tile into shared memory, completion
 //    tracked by mbarriers; a 12-stage ring keeps ~110 KB per SM in flight (16 MB chip-wide), which
 //    covers HBM3e latency at 6.5 TB/s.
 //  * one CTA per SM, 16 consumer warps in 4 groups (k-tiles are dealt round-robin to the groups)
