@@ -19,7 +19,7 @@ ENV_VARS = {
     "DLLAMA_PREFILL_TC_MIN_ROWS": ("128", "batch size from which prompt chunks use the tcgen05 attention kernel"),
     "DLLAMA_LAYERS_TC": ("1", "layer-list models in bf16: 0 = never use the tcgen05 GEMM (every product on the streaming / tiled kernels)"),
     "DLLAMA_LAYERS_ATTN_TC": ("1", "layer-list models in bf16: 0 = latent attention on the per-row kernel instead of the tensor-core one"),
-    "DLLAMA_LAYERS_CHUNKED_SCAN": ("1", "layer-list models: 0 = the Mamba-2 recurrence always token by token (no chunk-parallel passes for long portions)"),
+    "DLLAMA_LAYERS_CHUNKED_SCAN": ("1", "layer-list models: 0 = the Mamba-2 and lightning recurrences always token by token (no chunk-parallel passes for long portions)"),
     "DLLAMA_LAYERS_GRAPHS": ("1", "layer-list models: 0 = never replay decode-sized batches from CUDA graphs"),
     "DLLAMA_LAYERS_TC_MIN_ROWS": ("32", "layer-list models: batch size from which matrix products run on the tcgen05 GEMM"),
     # serving / tensor-parallel control
