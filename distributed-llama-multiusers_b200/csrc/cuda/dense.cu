@@ -6,18 +6,33 @@
 // load, so products are exact in f32 and only the accumulation order differs from a tensor-core product.
 //
 // Epilogues (what other models of this library fuse into their matmul kernels too): plain store, relu(.)^2,
-// aux * sigmoid(.) (an output gate), cap * tanh(. / cap) (logit soft-capping), . * sigmoid(.) (SiLU).
+// aux * sigmoid(.) (an output gate), cap * tanh(. / cap) (logit soft-capping), . * sigmoid(.) (SiLU), aux * (.) (the second
+// half of a gated unit), xIELU (a quadratic for z > 0, an exponential for z <= 0, two constants), and a sum into Y behind one
+// sigmoid gate per row.
 #include "layer_common.cuh"
 #include "../../../include/dllama_b200.h"
 
-__device__ __forceinline__ float dense_epi(float acc, int epi, float aux, float param) {
+__device__ __forceinline__ float dense_epi(float acc, int epi, float aux, float param, float param2) {
     switch (epi) {
         case DL_DENSE_RELU2: { const float r = fmaxf(acc, 0.f); return r * r; }
         case DL_DENSE_SIGMOID_MUL: return aux * sigmoid_f(acc);
         case DL_DENSE_SOFTCAP: return param * tanhf(acc / param);
         case DL_DENSE_SILU: return silu_f(acc);
+        case DL_DENSE_MUL: return aux * acc;
+        case DL_DENSE_XIELU: return acc > 0.f ? fmaf(param * acc, acc, 0.5f * acc) : fmaf(param2, expm1f(acc) - acc, 0.5f * acc);
         default: return acc;
     }
+}
+
+// element (m, n) of batch b leaves through the epilogue; the row-gated sum reads what Y holds first
+__device__ __forceinline__ void dense_store(const DlDenseArgs& a, int b, int m, int n, float acc) {
+    float* y = a.Y + (size_t)b * a.y_bs + (size_t)m * a.ldy + n;
+    if (a.epi == DL_DENSE_ROWGATE_ADD) {
+        *y = fmaf(sigmoid_f(a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux]), acc, *y);
+        return;
+    }
+    const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
+    *y = dense_epi(acc, a.epi, aux, a.param, a.param2);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -76,10 +91,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) dense_gemv_kernel(DlDenseArgs a
     if (lane == 0) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            if (m < a.M) {
-                const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
-                a.Y[(size_t)b * a.y_bs + (size_t)m * a.ldy + n] = dense_epi(acc[m], a.epi, aux, a.param);
-            }
+            if (m < a.M) dense_store(a, b, m, n, acc[m]);
         }
     }
 }
@@ -133,10 +145,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) dense_gemv_vec_kernel(DlDenseAr
     if (lane == 0) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            if (m < a.M) {
-                const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
-                a.Y[(size_t)b * a.y_bs + (size_t)m * a.ldy + n] = dense_epi(acc[m], a.epi, aux, a.param);
-            }
+            if (m < a.M) dense_store(a, b, m, n, acc[m]);
         }
     }
 }
@@ -196,8 +205,7 @@ __global__ void __launch_bounds__(256) dense_tile_kernel(DlDenseArgs a) {
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= a.N) continue;
-            const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
-            a.Y[(size_t)b * a.y_bs + (size_t)m * a.ldy + n] = dense_epi(acc[i][j], a.epi, aux, a.param);
+            dense_store(a, b, m, n, acc[i][j]);
         }
     }
 }
@@ -225,8 +233,8 @@ static void launch_dense(const DlDenseArgs& a, cudaStream_t st) {
 extern "C" int dl_dense(const DlDenseArgs* args, void* stream) {
     const DlDenseArgs& a = *args;
     if (a.M < 1 || a.N < 1 || a.K < 1 || a.batch < 1) { dl_set_error("dl_dense: empty problem"); return -1; }
-    if (a.epi == DL_DENSE_SIGMOID_MUL && a.aux == nullptr) { dl_set_error("dl_dense: the gate epilogue needs aux"); return -1; }
-    if (a.epi == DL_DENSE_GLU_CLAMP) { dl_set_error("dl_dense: the paired-column epilogue belongs to the tensor-core GEMM"); return -1; }
+    if ((a.epi == DL_DENSE_SIGMOID_MUL || a.epi == DL_DENSE_MUL || a.epi == DL_DENSE_ROWGATE_ADD) && a.aux == nullptr) { dl_set_error("dl_dense: the gate epilogue needs aux"); return -1; }
+    if (a.epi == DL_DENSE_GLU_CLAMP || a.epi == DL_DENSE_GLU_SILU) { dl_set_error("dl_dense: the paired-column epilogue belongs to the tensor-core GEMM"); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     if (a.wtype == DL_T_BF16) {
         if (a.round_x) launch_dense<__nv_bfloat16, true>(a, st);

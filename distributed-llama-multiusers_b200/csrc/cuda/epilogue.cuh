@@ -175,7 +175,7 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
         }
     } else if (e.kind == DL_EPI_DENSE) {
         // dense-weight models: an element-wise op on the f32 result, then a plain store (one destination)
-        if (e.dense_op == DL_DENSE_GLU_CLAMP) {
+        if (e.dense_op == DL_DENSE_GLU_CLAMP || e.dense_op == DL_DENSE_GLU_SILU) {
             // output rows interleaved (gate_j, up_j): thread j < rows/2 owns value j of the tile and stores column
             // grow0 / 2 + j:  a = min(gate, limit), b = clamp(up, +-limit), hidden = a * sigma(1.702 a) * (1 + b)
             const int col = (grow0 >> 1) + tid;
@@ -183,10 +183,12 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
                 const size_t ld = (size_t)e.ld;
                 float* d0 = e.dst[0] + (size_t)e.dst_off + (size_t)m0 * ld + col;
                 const float lim = e.dense_param;
+                const bool silu = e.dense_op == DL_DENSE_GLU_SILU;      // silu(gate) * up, no clamps
 #pragma unroll 4
                 for (int m = m_first; m < M; m += m_step) {
                     const float2 gu = *reinterpret_cast<const float2*>(out_s + m * out_ld + 2 * tid);
                     float g = gu.x, u = gu.y;
+                    if (silu) { d0[m * ld] = g / (1.0f + expf(-g)) * u; continue; }
                     if (lim > 0.0f) { g = fminf(g, lim); u = fminf(fmaxf(u, -lim), lim); }
                     d0[m * ld] = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
                 }
@@ -196,9 +198,10 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
             if (grow < d_real) {
                 const size_t ld = (size_t)e.ld, ald = (size_t)e.dense_aux_ld;
                 float* d0 = e.dst[0] + (size_t)e.dst_off + (size_t)m0 * ld + grow;
-                const float* aux = e.dense_aux != nullptr ? e.dense_aux + (size_t)m0 * ald + grow : nullptr;
                 const int op = e.dense_op;
-                const float prm = e.dense_param;
+                // one gate per row (ROWGATE_ADD) sits at aux[m * ald]; the other ops read aux[m * ald + column]
+                const float* aux = e.dense_aux != nullptr ? e.dense_aux + (size_t)m0 * ald + (op == DL_DENSE_ROWGATE_ADD ? 0 : grow) : nullptr;
+                const float prm = e.dense_param, prm2 = e.dense_param2;
 #pragma unroll 4
                 for (int m = m_first; m < M; m += m_step) {
                     float v = out_s[m * out_ld + tid];
@@ -206,6 +209,9 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
                     else if (op == DL_DENSE_SIGMOID_MUL) v = aux[m * ald] / (1.0f + expf(-v));
                     else if (op == DL_DENSE_SOFTCAP) v = prm * tanhf(v / prm);
                     else if (op == DL_DENSE_SILU) v = v / (1.0f + expf(-v));
+                    else if (op == DL_DENSE_MUL) v = aux[m * ald] * v;
+                    else if (op == DL_DENSE_XIELU) v = v > 0.0f ? fmaf(prm * v, v, 0.5f * v) : fmaf(prm2, expm1f(v) - v, 0.5f * v);
+                    else if (op == DL_DENSE_ROWGATE_ADD) v = fmaf(1.0f / (1.0f + expf(-aux[m * ald])), v, d0[m * ld]);
                     d0[m * ld] = v;
                 }
             }

@@ -3,6 +3,9 @@
 // per head.  Attention runs in the latent space ("absorbed" form):
 //     score_h(i, j) = scale * ( (U_k,h^T q_h,i) . c_j  +  qrot_h,i . krot_j )         softmax over j <= i
 //     out_h(i)      = U_v,h ( sum_j p_h(i, j) c_j )
+// Options: a sliding window (only i - j < window is visible; pages behind it are never read), a sink per head (one more
+// term exp(sink_h) in the softmax denominator, without a value) and a gate per row and head (the head's output leaves
+// multiplied by sigmoid(gate): a scalar commutes with the value up-projection that follows).
 // so the per-head work against the cache is a dot product with, and a weighted sum of, the same rows for every head.
 // The two per-head projections (U_k^T q before, U_v after) are batched dense products (dense.cu).
 //
@@ -40,10 +43,11 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(DlLatentKvArgs a) 
     for (int i = threadIdx.x; i < a.rank; i += blockDim.x) st_f(dst + i, in[i] * inv * a.norm_w[i]);
     const int half = a.rope_dims / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const int iu = a.interleaved ? 2 * i : i, iv = a.interleaved ? 2 * i + 1 : i + half;
         float u, v;
-        rot_pair(in[a.rank + i], in[a.rank + i + half], pos, a.freqs[i], u, v);
-        st_f(dst + a.rank + i, u);
-        st_f(dst + a.rank + i + half, v);
+        rot_pair(in[a.rank + iu], in[a.rank + iv], pos, a.freqs[i], u, v);
+        st_f(dst + a.rank + iu, u);
+        st_f(dst + a.rank + iv, v);
     }
     for (int i = a.rope_dims + threadIdx.x; i < a.rot; i += blockDim.x) st_f(dst + a.rank + i, in[a.rank + i]);
 }
@@ -110,14 +114,15 @@ __global__ void latent_attention_kernel(DlLatentAttnArgs a) {
     for (int t = threadIdx.x; t < H * R; t += blockDim.x) acc[t] = 0.f;
     for (int t = threadIdx.x; t < H; t += blockDim.x) { ml[2 * t] = -INFINITY; ml[2 * t + 1] = 0.f; }
     const int n_tiles = pos / LA_TILE + 1;
-    for (int t = 0; t < n_tiles; ++t) {
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;      // oldest visible position; pages before it are never read
+    for (int t = first / LA_TILE; t < n_tiles; ++t) {
         __syncthreads();                              // q_s / acc ready; previous tile consumed
         const int page = a.block_table[(size_t)slot * a.max_pages + t];
         const CT* src = (const CT*)a.cache + (size_t)page * LA_TILE * D;
-        const int valid = min(LA_TILE, pos + 1 - t * LA_TILE);
+        const int valid = min(LA_TILE, pos + 1 - t * LA_TILE), j_lo = max(0, first - t * LA_TILE);      // visible lines [j_lo, valid)
         for (int i = threadIdx.x; i < LA_TILE * D; i += blockDim.x) {
             const int j = i / D, d = i % D;
-            tile[j * DP + d] = j < valid ? ld_f(src + i) : 0.f;
+            tile[j * DP + d] = (j >= j_lo && j < valid) ? ld_f(src + i) : 0.f;
         }
         __syncthreads();
         for (int h = warp; h < H; h += nw) {
@@ -125,9 +130,10 @@ __global__ void latent_attention_kernel(DlLatentAttnArgs a) {
             const float* row = tile + lane * DP;
             float s = 0.f;
             for (int d = 0; d < D; ++d) s = fmaf(qh[d], row[d], s);
-            s = lane < valid ? s * a.scale : -INFINITY;
+            const bool vis = lane >= j_lo && lane < valid;
+            s = vis ? s * a.scale : -INFINITY;
             const float m_old = ml[2 * h], m_new = fmaxf(m_old, warp_max(s));
-            const float p = lane < valid ? expf(s - m_new) : 0.f;
+            const float p = vis ? expf(s - m_new) : 0.f;
             const float alpha = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
             const float l_new = ml[2 * h + 1] * alpha + warp_sum(p);
             p_s[warp * LA_TILE + lane] = p;
@@ -137,14 +143,21 @@ __global__ void latent_attention_kernel(DlLatentAttnArgs a) {
             const float* ps = p_s + warp * LA_TILE;
             for (int d = lane; d < R; d += 32) {
                 float v = ah[d] * alpha;
-                for (int j = 0; j < valid; ++j) v = fmaf(ps[j], tile[j * DP + d], v);
+                for (int j = j_lo; j < valid; ++j) v = fmaf(ps[j], tile[j * DP + d], v);
                 ah[d] = v;
             }
             __syncwarp();
         }
     }
     __syncthreads();
-    for (int t = threadIdx.x; t < H * R; t += blockDim.x) a.out[(size_t)m * H * R + t] = acc[t] / ml[2 * (t / R) + 1];
+    for (int t = threadIdx.x; t < H * R; t += blockDim.x) {
+        const int h = t / R;
+        float l = ml[2 * h + 1];
+        if (a.sink) l += expf(a.sink[h] - ml[2 * h]);
+        float v = acc[t] / l;
+        if (a.gate) v *= sigmoid_f(a.gate[(size_t)m * a.ld_gate + h]);
+        a.out[(size_t)m * H * R + t] = v;
+    }
 }
 
 static size_t latent_attention_smem(int H, int rank, int rot, int nw) {
@@ -227,9 +240,11 @@ __global__ void __launch_bounds__(32 * LQ_NJ * NI) latent_attention_mma_kernel(D
     const int qpos0 = pos0 + (mr0 < m_live ? mr0 / H : 0), qpos1 = pos0 + (mr1 < m_live ? mr1 / H : 0);
     const bool live0 = mr0 < m_live, live1 = mr1 < m_live;
     const int last_pos = pos0 + n_rows - 1;
+    const int pg_first = a.window > 0 ? max(0, pos0 - a.window + 1) / 32 : 0;      // pages before the first row's window are never read
     const int n_pages = last_pos / 32 + 1;
-    const int per = (n_pages + tl.n_splits - 1) / tl.n_splits;
-    const int p_begin = split * per, p_end = min(n_pages, p_begin + per);
+    const int per = (n_pages - pg_first + tl.n_splits - 1) / tl.n_splits;
+    const int p_begin = pg_first + split * per, p_end = min(n_pages, p_begin + per);
+    const int win = a.window > 0 ? a.window : 0x7fffffff;
     const int ks_per = Dp / LQ_NJ / 16;                  // k steps of this warp's share of D
     const int ocol0 = wj * NT * 8;                       // this warp's output columns
     // page `pg` -> buffer `buf`: lines past the last position and the padding columns are zeroed, the rest is copied
@@ -292,10 +307,10 @@ __global__ void __launch_bounds__(32 * LQ_NJ * NI) latent_attention_mma_kernel(D
                 v0.x += u0.x; v0.y += u0.y; v1.x += u1.x; v1.y += u1.y;
             }
             const int tok = pg * 32 + col;
-            p0[2 * e2] = (live0 && tok <= qpos0) ? v0.x * a.scale : -INFINITY;
-            p0[2 * e2 + 1] = (live0 && tok + 1 <= qpos0) ? v0.y * a.scale : -INFINITY;
-            p1[2 * e2] = (live1 && tok <= qpos1) ? v1.x * a.scale : -INFINITY;
-            p1[2 * e2 + 1] = (live1 && tok + 1 <= qpos1) ? v1.y * a.scale : -INFINITY;
+            p0[2 * e2] = (live0 && tok <= qpos0 && qpos0 - tok < win) ? v0.x * a.scale : -INFINITY;
+            p0[2 * e2 + 1] = (live0 && tok + 1 <= qpos0 && qpos0 - tok - 1 < win) ? v0.y * a.scale : -INFINITY;
+            p1[2 * e2] = (live1 && tok <= qpos1 && qpos1 - tok < win) ? v1.x * a.scale : -INFINITY;
+            p1[2 * e2 + 1] = (live1 && tok + 1 <= qpos1 && qpos1 - tok - 1 < win) ? v1.y * a.scale : -INFINITY;
             mx0 = fmaxf(mx0, fmaxf(p0[2 * e2], p0[2 * e2 + 1]));
             mx1 = fmaxf(mx1, fmaxf(p1[2 * e2], p1[2 * e2 + 1]));
         }
@@ -347,7 +362,10 @@ __global__ void __launch_bounds__(32 * LQ_NJ * NI) latent_attention_mma_kernel(D
             const int mr = half ? mr1 : mr0;
             if (mr >= m_live) continue;
             const int row = trows[mr / H], h = mr % H;
-            const float inv = 1.f / l_run[half];
+            float l = l_run[half];
+            if (a.sink) l += expf(a.sink[h] - m_run[half]);
+            float inv = 1.f / l;
+            if (a.gate) inv *= sigmoid_f(a.gate[(size_t)row * a.ld_gate + h]);
             float* dst = a.out + ((size_t)row * H + h) * R;
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
@@ -399,7 +417,9 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(DlLatentAttnArgs a, D
     __syncthreads();
     if ((int)threadIdx.x < ns) wgt[threadIdx.x] = wgt[threadIdx.x] == -INFINITY ? 0.f : expf(wgt[threadIdx.x] - mx);
     __syncthreads();
-    const float inv = 1.f / den;
+    if (a.sink) den += expf(a.sink[h] - mx);
+    float inv = 1.f / den;
+    if (a.gate) inv *= sigmoid_f(a.gate[(size_t)row * a.ld_gate + h]);
     for (int d = threadIdx.x; d < R; d += blockDim.x) {
         float acc = 0.f;
 #pragma unroll 8

@@ -1,9 +1,12 @@
 // Routed experts: every token runs `top` of `experts` small feed-forward layers  W_down act(W_up h),  act = relu(.)^2,
 // and sums their outputs weighted by the router's scores.  Gated experts (a third matrix W_gate per expert) use
-// hidden = a sigma(1.702 a) (1 + b) with a = min(gate . h, limit), b = clamp(up . h, +-limit) instead (sigma: logistic).
+// hidden = a sigma(1.702 a) (1 + b) with a = min(gate . h, limit), b = clamp(up . h, +-limit) instead (sigma: logistic), or
+// (gate_act 1) the plain gated unit hidden = silu(gate . h) (up . h).
 //
 // Routing (dl_moe_select), from the router logits z[M][experts] (a dense product, f32):  s = sigmoid(z), or s =
-// softmax(z) over all experts (`score` 1); the chosen weights may be multiplied by a constant (`scale`).  The experts
+// softmax(z) over all experts (`score` 1), z with an optional bias per expert added; the chosen weights may be multiplied
+// by a constant (`scale`).  Softmax scores divided by the sum of the chosen ones (`renorm`) are the softmax over the
+// chosen logits alone.  The experts
 // form `groups` equal groups of neighbours; a group's score is the sum of its `group_top` largest scores and only the
 // `keep` best groups stay eligible; the `top` eligible experts with the largest scores are chosen, their weights are
 // their scores (divided by the sum of the chosen scores if `renorm`).  Ties go to the lower index.  groups = keep = 1
@@ -47,16 +50,17 @@ __global__ void __launch_bounds__(MS_WARPS * 32) moe_select_kernel(DlMoeSelectAr
     float* s = sm + (size_t)warp * (2 * E + G);             // [E] scores, [E] working copy, [G] group scores (< 0: dropped)
     float* w = s + E;
     float* gs = w + E;
+    const float* zr = a.z + (size_t)m * a.ldz;
     if (a.score == 1) {                                     // softmax over all experts
         float mx = -INFINITY;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, a.z[(size_t)m * a.ldz + e]);
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e] + (a.bias ? a.bias[e] : 0.f));
         mx = warp_max(mx);
         float sum = 0.f;
-        for (int e = lane; e < E; e += 32) { const float p = expf(a.z[(size_t)m * a.ldz + e] - mx); s[e] = p; sum += p; }
+        for (int e = lane; e < E; e += 32) { const float p = expf(zr[e] + (a.bias ? a.bias[e] : 0.f) - mx); s[e] = p; sum += p; }
         sum = warp_sum(sum);
         for (int e = lane; e < E; e += 32) w[e] = s[e] = s[e] / sum;
     } else {
-        for (int e = lane; e < E; e += 32) w[e] = s[e] = sigmoid_f(a.z[(size_t)m * a.ldz + e]);
+        for (int e = lane; e < E; e += 32) w[e] = s[e] = sigmoid_f(zr[e] + (a.bias ? a.bias[e] : 0.f));
     }
     __syncwarp();
     if (G > 1) {
@@ -183,6 +187,10 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_up_rows_kernel(DlMoeArgs a,
     if (a.w_gate != nullptr) {                // gated: a sigma(1.702 a) (1 + b) on the clamped products
         const WT* wg = (const WT*)a.w_gate + ((size_t)e * a.ff + f) * a.width;
         float g = warp_dot<WT, RX>(wg, a.x + (size_t)m * a.ldx, a.width, vec, lane), u = v;
+        if (a.gate_act == 1) {                // silu(gate) * up
+            if (lane == 0) a.act[(size_t)pair * a.ff + f] = silu_f(g) * u;
+            return;
+        }
         if (a.limit > 0.f) { g = fminf(g, a.limit); u = fminf(fmaxf(u, -a.limit), a.limit); }
         if (lane == 0) a.act[(size_t)pair * a.ff + f] = g / (1.f + expf(-1.702f * g)) * (u + 1.f);
     } else if (lane == 0) {

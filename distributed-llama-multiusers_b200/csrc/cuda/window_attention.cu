@@ -75,47 +75,94 @@ __global__ void __launch_bounds__(256) window_kv_write_kernel(DlWindowKvArgs a) 
     }
 }
 
-// Separate values, no rotary: one CTA per row, a warp per (query or key) head.  With qk_norm every head is divided by
-// sqrt(mean(head^2) + eps): the queries in place, the keys on their way into the cache.  The values are copied behind
-// the keys.
+// Separate values: one CTA per row, a warp per (query or key) head.  Optional rotary on the first rope_dims dimensions
+// of every head (pairs (i, i + rope_dims / 2) with rope_half, else (2i, 2i + 1); cos and sin of the row's angles are
+// formed once, in f64), THEN, with qk_norm, every head is divided by sqrt(mean(head^2) + eps): the queries in place, the
+// keys on their way into the cache.  The values are copied behind the keys.  With `talk` the head mix of the scores is
+// folded into the queries: q_mixed[h][c * dim + i] = sum over the query heads g of key/value head c of talk[h][g] q_g[i].
+// Dynamic shared memory: (kv_heads + q_heads) * dim + rope_dims floats.
 template <typename CT>
 __global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
+    extern __shared__ float wk_sm[];
     const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int pos = a.pos[m], slot = a.slot[m];
     const int page = a.block_table[(size_t)slot * a.max_pages + pos / WA_PAGE];
-    const int LD = a.dim + a.vdim;
+    const int LD = a.dim + a.vdim, D = a.dim, RD = a.rope_dims, half = RD / 2;
     CT* line0 = (CT*)a.cache + (((size_t)page * a.kv_heads) * WA_PAGE + pos % WA_PAGE) * LD;
     const size_t head_step = (size_t)WA_PAGE * LD;
     const int nq = a.q ? a.q_heads : 0;
-    for (int h = warp; h < a.kv_heads + nq; h += nw) {
+    float* heads_s = wk_sm;                                   // [kv_heads + nq][D]: every head as it leaves (rotated, normalised)
+    float* cs = heads_s + (size_t)(a.kv_heads + nq) * D;      // [half] cos, then [half] sin
+    float* sn = cs + half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double sd, cd;
+        sincos((double)pos * a.freqs[i], &sd, &cd);
+        cs[i] = (float)(cd * (double)a.rope_scale);
+        sn[i] = (float)(sd * (double)a.rope_scale);
+    }
+    if (half > 0) __syncthreads();
+    for (int h = (a.k ? 0 : a.kv_heads) + warp; h < a.kv_heads + nq; h += nw) {      // without k (a layer that reads another layer's cache): the queries only
         const bool is_k = h < a.kv_heads;
-        float* qh = is_k ? nullptr : a.q + (size_t)m * a.ldq + (size_t)(h - a.kv_heads) * a.dim;
-        const float* src = is_k ? a.k + (size_t)m * a.ld + (size_t)h * a.dim : qh;
-        float inv = 1.f;
-        if (a.qk_norm) {
-            float ss = 0.f;
-            for (int i = lane; i < a.dim; i += 32) ss = fmaf(src[i], src[i], ss);
-            inv = 1.f / sqrtf(warp_sum(ss) / (float)a.dim + a.eps);
+        float* qh = is_k ? nullptr : a.q + (size_t)m * a.ldq + (size_t)(h - a.kv_heads) * D;
+        const float* src = is_k ? a.k + (size_t)m * a.ld + (size_t)h * D : qh;
+        float* hs = heads_s + (size_t)h * D;
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) {
+            float r = src[i];
+            if (i < RD) {
+                int p, iu, iv;
+                bool second;
+                if (a.rope_half) { p = i < half ? i : i - half; iu = p; iv = p + half; second = i >= half; }
+                else { p = i >> 1; iu = 2 * p; iv = iu + 1; second = i & 1; }
+                const float u = src[iu], v = src[iv];
+                r = second ? v * cs[p] + u * sn[p] : u * cs[p] - v * sn[p];
+            }
+            hs[i] = r;
+            ss = fmaf(r, r, ss);
         }
+        const float inv = a.qk_norm ? 1.f / sqrtf(warp_sum(ss) / (float)D + a.eps) : 1.f;
+        __syncwarp();                                         // every lane has read the head before it is rewritten in place
         if (is_k) {
             CT* dst = line0 + h * head_step;
-            for (int i = lane; i < a.dim; i += 32) st_f(dst + i, src[i] * inv);
-        } else if (a.qk_norm) {
-            for (int i = lane; i < a.dim; i += 32) qh[i] = src[i] * inv;
+            for (int i = lane; i < D; i += 32) st_f(dst + i, hs[i] * inv);
+        } else {
+            for (int i = lane; i < D; i += 32) { const float r = hs[i] * inv; hs[i] = r; qh[i] = r; }
         }
     }
-    for (int t = threadIdx.x; t < a.kv_heads * a.vdim; t += blockDim.x) {
+    for (int t = threadIdx.x; a.v != nullptr && t < a.kv_heads * a.vdim; t += blockDim.x) {
         const int g = t / a.vdim, i = t - g * a.vdim;
         st_f(line0 + g * head_step + a.dim + i, a.v[(size_t)m * a.ldv + t]);
+    }
+    if (a.talk != nullptr && nq > 0) {
+        __syncthreads();
+        const int rep = nq / a.kv_heads, QD = a.kv_heads * D;
+        const float* qs = heads_s + (size_t)a.kv_heads * D;
+        for (int t = threadIdx.x; t < nq * QD; t += blockDim.x) {
+            const int h = t / QD, c = (t - h * QD) / D, i = t - h * QD - c * D;
+            float acc = 0.f;
+            for (int g = c * rep; g < (c + 1) * rep; ++g) acc = fmaf(a.talk[h * nq + g], qs[(size_t)g * D + i], acc);
+            a.q_mixed[(size_t)m * a.ld_qm + t] = acc;
+        }
     }
 }
 
 extern "C" int dl_window_kv_write(const DlWindowKvArgs* args, int M, void* stream) {
     const DlWindowKvArgs& a = *args;
-    if (a.v != nullptr) {
-        if (a.rope_dims != 0 || a.vdim < 1 || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: separate values come without rotary (rope_dims %d, vdim %d)", a.rope_dims, a.vdim); return -1; }
-        if (a.ctype == DL_T_BF16) attn_kv_write_kernel<__nv_bfloat16><<<M, 256, 0, (cudaStream_t)stream>>>(a);
-        else attn_kv_write_kernel<float><<<M, 256, 0, (cudaStream_t)stream>>>(a);
+    if (a.vdim > 0) {
+        if ((a.k == nullptr) != (a.v == nullptr) || (a.k == nullptr && a.q == nullptr)) { dl_set_error("dl_window_kv_write: keys and values come together, or the queries alone"); return -1; }
+        if (a.rope_dims < 0 || a.rope_dims > a.dim || (a.rope_dims & 1) || a.vdim < 1 || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: bad sizes (rope_dims %d, dim %d, vdim %d)", a.rope_dims, a.dim, a.vdim); return -1; }
+        if (a.talk != nullptr && (a.q == nullptr || a.q_mixed == nullptr || a.q_heads % a.kv_heads)) { dl_set_error("dl_window_kv_write: the head mix needs q, q_mixed and whole groups of heads"); return -1; }
+        const size_t smem = ((size_t)(a.kv_heads + (a.q ? a.q_heads : 0)) * a.dim + a.rope_dims) * sizeof(float);
+        if (smem > 227 * 1024) { dl_set_error("dl_window_kv_write: %zu bytes of shared memory", smem); return -1; }
+        cudaError_t e;
+        if (a.ctype == DL_T_BF16) {
+            e = cudaFuncSetAttribute(attn_kv_write_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess) attn_kv_write_kernel<__nv_bfloat16><<<M, 256, smem, (cudaStream_t)stream>>>(a);
+        } else {
+            e = cudaFuncSetAttribute(attn_kv_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess) attn_kv_write_kernel<float><<<M, 256, smem, (cudaStream_t)stream>>>(a);
+        }
+        if (e != cudaSuccess) { dl_set_error("dl_window_kv_write: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
         LAYER_CHECK_LAUNCH("dl_window_kv_write");
         return 0;
     }
@@ -136,17 +183,18 @@ __global__ void window_attention_kernel(DlWindowAttnArgs a) {
     extern __shared__ float sm[];
     const int m = blockIdx.x, g = blockIdx.y;
     const int rep = a.heads / a.kv_heads, D = a.dim, RD = a.rope_dims, DV = a.vdim > 0 ? a.vdim : D;
-    const int LD = D + (a.vdim > 0 ? a.vdim : RD), LP = LD + 1;
+    const int KH = a.key_heads > 1 ? a.key_heads : 1, QD = KH * D;      // head-mixed scores: a query meets the keys of all KH key/value heads side by side
+    const int LD = D + (a.vdim > 0 ? a.vdim : RD), VT = LD - D, LP = QD + VT + 1;
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* q_s = sm;                                   // [rep][D]
-    float* tile = q_s + (size_t)rep * D;               // [WA_PAGE][LD + 1]
+    float* q_s = sm;                                   // [rep][QD]
+    float* tile = q_s + (size_t)rep * QD;              // [WA_PAGE][QD keys | VT: the rest of head g's line | 1]
     float* acc = tile + (size_t)WA_PAGE * LP;          // [rep][DV]
     float* p_s = acc + (size_t)rep * DV;               // [nw][WA_PAGE]
     float* ml = p_s + (size_t)nw * WA_PAGE;            // [rep][2]
     const int pos = a.pos[m], slot = a.slot[m];
     int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;            // oldest visible position
     if (a.chunk > 0) first = max(first, pos / a.chunk * a.chunk);
-    for (int t = threadIdx.x; t < rep * D; t += blockDim.x) q_s[t] = a.q[(size_t)m * a.ldq + (size_t)g * rep * D + t];
+    for (int t = threadIdx.x; t < rep * QD; t += blockDim.x) q_s[t] = a.q[(size_t)m * a.ldq + (size_t)g * rep * QD + t];
     for (int t = threadIdx.x; t < rep * DV; t += blockDim.x) acc[t] = 0.f;
     for (int t = threadIdx.x; t < rep; t += blockDim.x) { ml[2 * t] = -INFINITY; ml[2 * t + 1] = 0.f; }
     for (int pg = first / WA_PAGE; pg <= pos / WA_PAGE; ++pg) {
@@ -156,15 +204,23 @@ __global__ void window_attention_kernel(DlWindowAttnArgs a) {
         const int j_lo = max(0, first - pg * WA_PAGE), j_hi = min(WA_PAGE, pos + 1 - pg * WA_PAGE);   // visible lines [j_lo, j_hi)
         for (int i = threadIdx.x; i < WA_PAGE * LD; i += blockDim.x) {
             const int j = i / LD, d = i - j * LD;
-            tile[j * LP + d] = (j >= j_lo && j < j_hi) ? ld_f(src + i) : 0.f;
+            if (KH > 1 && d < D) continue;             // the keys come from every key/value head, below
+            tile[j * LP + (d < D ? d : QD + d - D)] = (j >= j_lo && j < j_hi) ? ld_f(src + i) : 0.f;
+        }
+        if (KH > 1) {
+            for (int i = threadIdx.x; i < KH * WA_PAGE * D; i += blockDim.x) {
+                const int c = i / (WA_PAGE * D), j = (i - c * WA_PAGE * D) / D, d = i - (c * WA_PAGE + j) * D;
+                const CT* kc = (const CT*)a.cache + (((size_t)page * a.kv_heads + c) * WA_PAGE + j) * LD;
+                tile[j * LP + c * D + d] = (j >= j_lo && j < j_hi) ? ld_f(kc + d) : 0.f;
+            }
         }
         __syncthreads();
         for (int h = warp; h < rep; h += nw) {
-            const float* qh = q_s + (size_t)h * D;
+            const float* qh = q_s + (size_t)h * QD;
             const float* row = tile + lane * LP;
             const bool vis = lane >= j_lo && lane < j_hi;
             float s = 0.f;
-            for (int d = 0; d < D; ++d) s = fmaf(qh[d], row[d], s);
+            for (int d = 0; d < QD; ++d) s = fmaf(qh[d], row[d], s);
             s *= a.scale;
             if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
             if (!vis) s = -INFINITY;
@@ -178,7 +234,7 @@ __global__ void window_attention_kernel(DlWindowAttnArgs a) {
             float* ah = acc + (size_t)h * DV;
             const float* ps = p_s + warp * WA_PAGE;
             for (int d = lane; d < DV; d += 32) {
-                const int col = (a.vdim > 0 || d < RD) ? D + d : d;      // own values, or the value's first entries, sit behind the key
+                const int col = (a.vdim > 0 || d < RD) ? QD + d : d;     // own values, or the value's first entries, sit behind the key
                 float v = ah[d] * alpha;
                 for (int j = j_lo; j < j_hi; ++j) v = fmaf(ps[j], tile[j * LP + col], v);
                 ah[d] = v;
@@ -197,7 +253,7 @@ __global__ void window_attention_kernel(DlWindowAttnArgs a) {
 
 static int window_args_ok(const DlWindowAttnArgs& a, const char* who) {
     if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.rope_dims > a.dim || a.window < 0 || a.page_size != WA_PAGE ||
-        a.vdim < 0 || a.chunk < 0 || (a.vdim > 0 && a.rope_dims != 0)) {
+        a.vdim < 0 || a.chunk < 0 || (a.vdim > 0 && a.rope_dims != 0) || (a.key_heads > 1 && (a.key_heads != a.kv_heads || a.vdim < 1))) {
         dl_set_error("%s: bad shape (heads %d / %d, dim %d, rotary %d, window %d, page %d)", who, a.heads, a.kv_heads, a.dim, a.rope_dims, a.window, a.page_size);
         return -1;
     }
@@ -208,7 +264,8 @@ extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* st
     const DlWindowAttnArgs& a = *args;
     if (window_args_ok(a, "dl_window_attention")) return -1;
     const int rep = a.heads / a.kv_heads, nw = rep < 8 ? rep : 8, LD = a.dim + (a.vdim > 0 ? a.vdim : a.rope_dims), DV = a.vdim > 0 ? a.vdim : a.dim;
-    const size_t smem = ((size_t)rep * (a.dim + DV) + (size_t)WA_PAGE * (LD + 1) + (size_t)nw * WA_PAGE + 2 * (size_t)rep) * sizeof(float);
+    const int QD = (a.key_heads > 1 ? a.key_heads : 1) * a.dim;
+    const size_t smem = ((size_t)rep * (QD + DV) + (size_t)WA_PAGE * (QD + LD - a.dim + 1) + (size_t)nw * WA_PAGE + 2 * (size_t)rep) * sizeof(float);
     if (smem > 227 * 1024) { dl_set_error("dl_window_attention: %d heads per group x dim %d need %zu bytes of shared memory", rep, a.dim, smem); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(M, a.kv_heads);
@@ -513,6 +570,7 @@ extern "C" int dl_window_attention_tc(const DlWindowAttnArgs* args, const int* t
                                       float* partial, void* stream) {
     const DlWindowAttnArgs& a = *args;
     if (window_args_ok(a, "dl_window_attention_tc")) return -1;
+    if (a.key_heads > 1) { dl_set_error("dl_window_attention_tc: head-mixed scores run on dl_talk_attention_tc"); return -1; }
     if (a.vdim > 0 && a.vdim != a.dim) { dl_set_error("dl_window_attention_tc: values of their own must be as wide as the keys (dim %d, vdim %d)", a.dim, a.vdim); return -1; }
     if (dl_window_attention_tc_supported(a.heads, a.kv_heads, a.dim, a.rope_dims, a.ctype) != 0 || rq < 1 || rq > dl_window_tc_rows(a.heads, a.kv_heads) ||
         (a.ldq & 3) || (a.ldo & 1) || ((uintptr_t)a.q & 15)) {

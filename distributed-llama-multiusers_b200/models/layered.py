@@ -6,6 +6,8 @@ meets the residual stream is the architecture's ``residual`` style (``RESIDUAL_S
     "hyper":     u = sum_s in[s] x_s;  y = sub(norm(u));  x_t <- sum_s mix[s][t] x_s + m out[t] y      (Sunesun)
                  `streams` copies of the stream (hyper-connections); without them the plain x <- x + m sub(norm(x)),
                  which is how Venadra's pre-norm layers run (one stream, m = 1)
+    "post":      x <- x + m * norm(sub(x))                               the sublayer reads the stream itself; the only
+                 norm sits on its output (Darusun)
 
 What a design fixes without saying it in config.json (how its attention masks, whether its experts are gated, ...) is
 its entry of ``DESIGNS``; everything config.json gives is read from there.  A configuration with ``canon: {taps}`` puts a
@@ -22,12 +24,15 @@ this engine.  Mixers here:
 * ``attention`` -- grouped-query attention over a paged cache of one line per token and key/value head.  Per design:
   values that are the keys (one projection) or have a projection of their own; a sliding window or a chunked mask;
   interleaved rotary positions with optional frequency interpolation, or none; soft-capped scores; queries and keys
-  divided by their root mean square; a sink per head in the softmax denominator; a sigmoid output gate;
+  divided by their root mean square; a sink per head in the softmax denominator; a sigmoid output gate; rotary in the
+  rotate-half layout in front of the unit norm; scores mixed across heads by a matrix `talk` before the softmax (folded
+  into the queries, see WindowAttentionMixer); a layer that reads another layer's keys and values (``kv_from``);
 * ``lightning`` -- linear attention with a fixed decay per head and an f32 state [dim][vdim] per head and slot, SiLU on
   q, k and v, an RMS norm over the concatenated heads and a sigmoid output gate.
 
-Feed-forwards: ``dense`` (squared ReLU, or PolyNorm) and ``moe`` (sigmoid-scored, group-limited routing over small
-squared-ReLU experts; or softmax-scored, renormalised routing over gated experts).  A layer with ``weights_of: j`` runs
+Feed-forwards: ``dense`` (squared ReLU, PolyNorm, or xIELU) and ``moe`` (sigmoid-scored, group-limited routing over small
+squared-ReLU experts; or softmax-scored, renormalised routing over gated experts, with an optional router bias and a
+shared expert behind a sigmoid gate per token).  A layer with ``weights_of: j`` runs
 layer j's weights on a cache or state of its own (a looped layer).
 
 What the engine shares with ``LlamaEngine`` is the serving surface (slots, rows with per-row positions, paged token
@@ -68,7 +73,12 @@ class LayerSpec:
 # What a design fixes outside its config.json, by architecture name.  residual: how sublayers meet the residual stream.
 # attention: values ("keys": the keys as projected | "own": a projection v), mask (what mask.size means: "window" |
 # "chunk"), qk_norm, sink (tensor `sink` [heads]), gate (tensor `g`: sigmoid output gate).  dense_act: "relu2" |
-# "polynorm" (tensor `act` [4]).  moe: score ("sigmoid" | "softmax"), renorm, gated (tensors e<n>.gate; expert.limit).
+# "polynorm" (tensor `act` [4]) | "xielu" (tensor `act` [2]).  moe: score ("sigmoid" | "softmax"), renorm, gated (tensors
+# e<n>.gate; True: a sigma(1.702 a) (1 + b) with expert.limit, "silu": silu(a) b), bias (tensor `router.b`), shared (entry
+# `shared` of the mlp: one more gated expert for every token behind sigmoid(`shared.sg` . h)).  attention also: rot
+# ("interleaved" | "half": the pair layout of the rotary, which own values otherwise exclude), talk (tensor `talk`
+# [heads][heads] mixes the scores of the heads before the softmax).  latent: rot (the same), sink, gate ("full": one
+# gate per output column | "head": one per head).  norm_weights "scalar": every norm over the width has one number.
 DESIGNS = {
     "Ribivik": {"residual": "sandwich"},
     "Sunesun": {"residual": "hyper"},
@@ -76,6 +86,11 @@ DESIGNS = {
                 "attention": {"values": "own", "mask": "chunk", "qk_norm": True, "sink": True, "gate": True},
                 "dense_act": "polynorm",
                 "moe": {"score": "softmax", "renorm": True, "gated": True}},
+    "Darusun": {"residual": "post", "norm_weights": "scalar",
+                "attention": {"values": "own", "qk_norm": True, "rot": "half", "talk": True},
+                "latent": {"rot": "interleaved", "sink": True, "gate": "head"},
+                "dense_act": "xielu",
+                "moe": {"score": "softmax", "renorm": True, "gated": "silu", "bias": True, "shared": True}},
 }
 RESIDUAL_STYLES = {name: d["residual"] for name, d in DESIGNS.items()}
 
@@ -91,7 +106,7 @@ class LayerListConfig:
     seq_len: int = 0
     residual: str = "sandwich"
     embed_scale: float = 1.0               # the embedding output is multiplied by it
-    residual_mult: float = 1.0             # "hyper": every sublayer output is multiplied by it on its way into the stream
+    residual_mult: float = 1.0             # "hyper", "post": every sublayer output is multiplied by it on its way into the stream
     streams: int = 1                       # "hyper": copies of the residual stream
     hyper_weights: bool = False            # the layers bring hc<q>.in / .out / .mix tensors (else the plain sum)
     canon_taps: int = 0                    # > 0: h <- h + conv(h) over the last `taps` normed inputs, in front of every mixer
@@ -190,10 +205,16 @@ WINDOW_CTAS_PER_SM = 8       # pages are shared until about this many CTAs per S
 class LatentAttentionMixer:
     """Tensors <prefix>dq, dq.norm, uq, [dkv, dkv.norm], uk, uv, g, o.  Sizes from the layer's mixer entry: heads, dim
     (unrotated query / key dims per head), rot_dim (rotated dims per head, one shared key part), vdim, q_rank, kv_rank,
-    scale, rot {base, dims}, and kv_from (index of the layer whose cache this one reads)."""
+    scale, rot {base, dims}, mask.size (a sliding window; absent: all earlier positions) and kv_from (index of the layer
+    whose cache this one reads).  The design's `latent` traits: rot "half" (default: dimension i pairs with i + dims / 2) |
+    "interleaved" (2i with 2i + 1); sink: <prefix>sink [heads] joins the softmax denominator; gate "full" (default: <prefix>g
+    [heads * vdim][width], one gate per output column) | "head" (<prefix>g [heads][width], one sigmoid gate per head)."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng, self.index = eng, index
+        tr = eng.cfg.traits.get("latent") or {}
+        self.interleaved, self.head_gate = tr.get("rot", "half") == "interleaved", tr.get("gate", "full") == "head"
+        self.window = int((m.get("mask") or {}).get("size") or 0)
         self.H, self.dn, self.dr, self.dv = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
         self.q_rank, self.rank = int(m["q_rank"]), int(m["kv_rank"])
         self.scale = float(m["scale"])
@@ -206,6 +227,11 @@ class LatentAttentionMixer:
         self.w_dq, self.dq_norm, self.w_uq = D(W(prefix + "dq")), V(prefix + "dq.norm"), D(W(prefix + "uq"))
         self.w_g, self.w_o = D(W(prefix + "g")), D(W(prefix + "o"))
         H, dn, dv, r = self.H, self.dn, self.dv, self.rank
+        if tuple(self.w_g.t.shape) != ((H if self.head_gate else H * dv), eng.cfg.width):
+            raise ValueError(f"layer {index}: g has shape {tuple(self.w_g.t.shape)}")
+        self.sink = V(prefix + "sink") if tr.get("sink") else None
+        if self.sink is not None and tuple(self.sink.shape) != (H,):
+            raise ValueError(f"layer {index}: sink has shape {tuple(self.sink.shape)}")
         # key up-projection per head, transposed, so that  q_lat[h] = U_k,h^T q_h  is a product against rows of K = dn
         self.w_uk_t = D(W(prefix + "uk").reshape(H, dn, r).transpose(1, 2).contiguous())
         self.w_uv = D(W(prefix + "uv").reshape(H, dv, r).contiguous())
@@ -218,14 +244,14 @@ class LatentAttentionMixer:
     def scratch(self) -> Dict[str, int]:
         H = self.H
         return {"cq": self.q_rank, "q": H * (self.dn + self.dr), "kv": self.rank + self.dr, "q_lat": H * self.rank,
-                "o_lat": H * self.rank, "o": H * self.dv, "og": H * self.dv}
+                "o_lat": H * self.rank, "o": H * self.dv, "og": H * self.dv, "gz": H}
 
     def bind(self, mixers: list):
         if self.kv_from is not None:
             src = mixers[int(self.kv_from)]
             if not isinstance(src, LatentAttentionMixer) or src.kv_from is not None:
                 raise ValueError(f"layer {self.index}: kv_from {self.kv_from} is not a layer with a cache of its own")
-            if (src.rank, src.dr, src.rope_dims) != (self.rank, self.dr, self.rope_dims):
+            if (src.rank, src.dr, src.rope_dims, src.interleaved) != (self.rank, self.dr, self.rope_dims, self.interleaved):
                 raise ValueError(f"layer {self.index}: cache shape differs from layer {self.kv_from}")
             self.cache = src.cache
 
@@ -242,16 +268,23 @@ class LatentAttentionMixer:
         e.mm(self.w_dq, h, cq, M, src="h")
         L.rms_norm(cq, cq, M, self.q_rank, e.cfg.norm_eps, w=self.dq_norm)
         e.mm(self.w_uq, cq, q, M)
-        L.rope_rows(q, M, H, hd, dn, self.rope_dims, self.freqs, e.pos)
+        L.rope_rows(q, M, H, hd, dn, self.rope_dims, self.freqs, e.pos, interleaved=self.interleaved)
         if self.kv_from is None:
             kv = e.buf("kv")
             e.mm(self.w_dkv, h, kv, M, src="h")
             L.latent_kv_write(kv, M, self.dkv_norm, e.cfg.norm_eps, r, dr, self.rope_dims, self.freqs, e.pos, e.slot,
-                              e.block_table, self.cache)
+                              e.block_table, self.cache, interleaved=self.interleaved)
         e.mm_heads(self.w_uk_t, q, q_lat, M, hd, r)
+        gz = None
+        if self.head_gate:          # one gate per head: a scalar commutes with the value up-projection, so the attention kernel applies it
+            gz = e.buf("gz", H)
+            e.mm(self.w_g, h, gz, M, src="h")
         L.latent_attention(q_lat, q, hd, dn, o_lat, M, H, r, dr, self.scale, e.pos, e.slot, e.block_table, self.cache,
-                           tiles=e.latent_tiles(self))
+                           tiles=e.latent_tiles(self), window=self.window, sink=self.sink, gate=gz)
         e.mm_heads(self.w_uv, o_lat, o, M, r, dv)
+        if self.head_gate:
+            e.mm(self.w_o, o, y, M)
+            return
         e.mm(self.w_g, h, og, M, epi=L.DENSE_SIGMOID_MUL, aux=o, src="h")
         e.mm(self.w_o, og, y, M)
 
@@ -303,15 +336,24 @@ class Mamba2Mixer:
 class DenseFeedForward:
     """Tensors <prefix>up, down:  W_down act(W_up h).  act = relu(.)^2, or (design trait dense_act "polynorm", tensor
     <prefix>act = [c1, c2, c3, c0]) PolyNorm: c0 + sum_p cp z^p / rms(z^p), p = 1..3, with the powers taken element-wise and
-    the root mean square (eps inside) over a row."""
+    the root mean square (eps inside) over a row; or ("xielu", tensor <prefix>act = [p, q]) xIELU: softplus(p) z^2 + z / 2 for
+    z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 for z <= 0, in the up-projection's epilogue."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng = eng
         self.ff = int(m["ff"])
         self.w_up, self.w_down = eng.dense_weight(eng.weight(prefix + "up")), eng.dense_weight(eng.weight(prefix + "down"))
-        self.poly = eng.vector(prefix + "act") if eng.cfg.traits.get("dense_act") == "polynorm" else None
+        act = eng.cfg.traits.get("dense_act")
+        self.poly = eng.vector(prefix + "act") if act == "polynorm" else None
         if self.poly is not None and tuple(self.poly.shape) != (4,):
             raise ValueError(f"layer {index}: {prefix}act has shape {tuple(self.poly.shape)}")
+        self.xielu = None
+        if act == "xielu":          # tensor act = [p, q]: the two constants softplus(p) and 1/2 + softplus(q), formed once in f32
+            pq = eng.vector(prefix + "act")
+            if tuple(pq.shape) != (2,):
+                raise ValueError(f"layer {index}: {prefix}act has shape {tuple(pq.shape)}")
+            sp = torch.nn.functional.softplus(pq.float().cpu())
+            self.xielu = (float(sp[0]), float(torch.tensor(0.5, dtype=torch.float32) + sp[1]))
 
     def scratch(self) -> Dict[str, int]:
         return {"up": self.ff}
@@ -325,6 +367,8 @@ class DenseFeedForward:
         if self.poly is not None:
             e.mm(self.w_up, h, up, M, src="h")
             L.poly_norm(up, up, M, self.ff, self.poly, e.cfg.norm_eps)
+        elif self.xielu is not None:
+            e.mm(self.w_up, h, up, M, epi=L.DENSE_XIELU, param=self.xielu[0], param2=self.xielu[1], src="h")
         else:
             e.mm(self.w_up, h, up, M, epi=L.DENSE_RELU2, src="h")
         e.mm(self.w_down, up, y, M)
@@ -341,7 +385,15 @@ class WindowAttentionMixer:
       mask "chunk": position i sees j <= i with floor(j / size) = floor(i / size): chunk borders are multiples of size in sequence positions;
       qk_norm: every query and key head is divided by its root mean square (eps of the model) before the scores;
       sink: <prefix>sink [heads], exp(sink_h) joins the softmax denominator without a key or a value;
-      gate: <prefix>g, the concatenated heads are multiplied by sigmoid(W_g h) before the output projection."""
+      gate: <prefix>g, the concatenated heads are multiplied by sigmoid(W_g h) before the output projection;
+      rot "half" | "interleaved" with values "own": rotary on the first rot.dims dimensions of every query and key head in
+             that pair layout, BEFORE the unit norm;
+      talk: <prefix>talk [heads][heads] mixes the heads' scaled scores before mask and softmax, score'_h = sum_g talk[h][g]
+             score_g.  The mix is linear in the queries, so it is folded into them: with c(g) the key/value head of query
+             head g,  score'_h = sum_c ( sum_{g: c(g) = c} talk[h][g] q_g ) . k_c  -- head h gets ONE query of kv_heads * dim
+             numbers that meets the keys of all key/value heads side by side; the values stay those of its own group.
+    A mixer entry with `kv_from: j` has no k / v tensors and no cache: it reads layer j's keys (as cached: rotated and
+    normalised) and values with queries, mask and the rest of its own."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str, share: Optional["WindowAttentionMixer"] = None):
         self.eng, self.index = eng, index
@@ -358,18 +410,23 @@ class WindowAttentionMixer:
         self.window, self.chunk = (0, size) if tr.get("mask", "window") == "chunk" else (size, 0)
         rot = m.get("rot") or {"base": 10000.0, "dims": 0}
         self.rope_dims = int(rot["dims"])
-        if self.rope_dims > self.dim or self.rope_dims % 2 or (self.own_v and self.rope_dims):
+        self.own_rot = tr.get("rot")                      # own values: the pair layout of the rotary (None: no rotary with own values)
+        self.kv_from = m.get("kv_from")
+        if self.rope_dims > self.dim or self.rope_dims % 2 or (self.own_v and self.rope_dims and self.own_rot not in ("half", "interleaved")):
             raise ValueError(f"layer {index}: rotary dims {self.rope_dims} do not fit dim {self.dim}")
+        if self.kv_from is not None and (not self.own_v or share is not None):
+            raise ValueError(f"layer {index}: kv_from is known for attention with values of its own and weights of its own")
         freqs, self.rope_mag = interpolated_rotary(float(rot["base"]), self.rope_dims, rot.get("scaling"))
         self.freqs = freqs.to(eng.device) if self.rope_dims else torch.zeros(1, dtype=torch.float64, device=eng.device)
         H, G, d, dv = self.H, self.G, self.dim, self.vdim
         if share is None:
             W, D = eng.weight, eng.dense_weight
-            wq, wk = W(prefix + "q"), W(prefix + "k")
-            if tuple(wq.shape) != (H * d, eng.cfg.width) or tuple(wk.shape) != (G * d, eng.cfg.width):
-                raise ValueError(f"layer {index}: q / k have shapes {tuple(wq.shape)} / {tuple(wk.shape)}")
-            parts = [wq, wk]
-            if self.own_v:
+            wq = W(prefix + "q")
+            wk = W(prefix + "k") if self.kv_from is None else None
+            if tuple(wq.shape) != (H * d, eng.cfg.width) or (wk is not None and tuple(wk.shape) != (G * d, eng.cfg.width)):
+                raise ValueError(f"layer {index}: q / k have shapes {tuple(wq.shape)} / {tuple(wk.shape) if wk is not None else None}")
+            parts = [wq] + ([wk] if wk is not None else [])
+            if self.own_v and self.kv_from is None:
                 wv = W(prefix + "v")
                 if tuple(wv.shape) != (G * dv, eng.cfg.width):
                     raise ValueError(f"layer {index}: v has shape {tuple(wv.shape)}")
@@ -380,26 +437,38 @@ class WindowAttentionMixer:
             self.sink = eng.vector(prefix + "sink") if tr.get("sink") else None
             if self.sink is not None and tuple(self.sink.shape) != (H,):
                 raise ValueError(f"layer {index}: sink has shape {tuple(self.sink.shape)}")
+            self.talk = eng.vector(prefix + "talk") if tr.get("talk") else None
+            if self.talk is not None and tuple(self.talk.shape) != (H, H):
+                raise ValueError(f"layer {index}: talk has shape {tuple(self.talk.shape)}")
         else:
-            self.w_qk, self.w_o, self.w_g, self.sink = share.w_qk, share.w_o, share.w_g, share.sink
+            self.w_qk, self.w_o, self.w_g, self.sink, self.talk = share.w_qk, share.w_o, share.w_g, share.sink, share.talk
         self.owns_weights = share is None
         self.line = d + (dv if self.own_v else self.rope_dims)
-        self.cache = torch.zeros(eng.n_pages, G, PAGE, self.line, dtype=eng.wdtype, device=eng.device)
+        # a kv_from layer is bound to its owner's cache once all layers exist
+        self.cache = torch.zeros(eng.n_pages, G, PAGE, self.line, dtype=eng.wdtype, device=eng.device) if self.kv_from is None else None
         # bf16 caches of sizes the tensor-core kernel takes: tiles of tc_rq consecutive rows of a sequence (0: per-row kernel)
         L = eng.L
         self.tc_rq = 0
-        if eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0" and dv == d and \
-                L.window_tc_supported(H, G, d, self.rope_dims, eng.wdtype):
+        if eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0" and dv == d and self.talk is None and \
+                L.window_tc_supported(H, G, d, 0 if self.own_v else self.rope_dims, eng.wdtype):
             self.tc_rq = L.window_tc_rows(H, G)
 
     def scratch(self) -> Dict[str, int]:
         n = {"qk": (self.H + self.G) * self.dim + (self.G * self.vdim if self.own_v else 0), "o": self.H * self.vdim}
         if self.w_g is not None:
             n["og"] = self.H * self.vdim
+        if self.talk is not None:
+            n["qmix"] = self.H * self.G * self.dim
         return n
 
     def bind(self, mixers: list):
-        pass
+        if self.kv_from is not None:
+            src = mixers[int(self.kv_from)]
+            if not isinstance(src, WindowAttentionMixer) or src.kv_from is not None:
+                raise ValueError(f"layer {self.index}: kv_from {self.kv_from} is not an attention layer with a cache of its own")
+            if (src.G, src.dim, src.vdim, src.rope_dims, src.own_v) != (self.G, self.dim, self.vdim, self.rope_dims, self.own_v):
+                raise ValueError(f"layer {self.index}: key / value shapes differ from layer {self.kv_from}")
+            self.cache = src.cache
 
     def weight_bytes(self) -> int:
         if not self.owns_weights:
@@ -410,16 +479,24 @@ class WindowAttentionMixer:
         e, L = self.eng, self.eng.L
         H, G, d, dv, rd = self.H, self.G, self.dim, self.vdim, self.rope_dims
         nqk = (H + G) * d
-        qk, o = e.buf("qk", nqk + (G * dv if self.own_v else 0)), e.buf("o", H * dv)
+        own_kv = self.kv_from is None
+        qk, o = e.buf("qk", self.w_qk.N), e.buf("o", H * dv)
         e.mm(self.w_qk, h, qk, M, src="h")
-        # one launch: the keys (and values) go into the cache and the queries are rotated / normalised in place
+        # one launch: the keys (and values) go into the cache and the queries are rotated / normalised in place (and mixed)
+        q_in = qk
         if self.own_v:
-            L.window_kv_write(qk[:, H * d:], M, G, d, 0, self.freqs, 1.0, e.pos, e.slot, e.block_table, self.cache, q=qk, q_heads=H,
-                              v=qk[:, nqk:], vdim=dv, qk_norm=self.qk_norm, eps=e.cfg.norm_eps)
+            if self.talk is not None:
+                q_in = e.buf("qmix", H * G * d)
+            L.window_kv_write(qk[:, H * d:] if own_kv else None, M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table,
+                              self.cache, q=qk, q_heads=H, v=qk[:, nqk:] if own_kv else None, vdim=dv, qk_norm=self.qk_norm,
+                              eps=e.cfg.norm_eps, rope_half=self.own_rot == "half", talk=self.talk, q_mixed=q_in if self.talk is not None else None)
+            rd = 0                            # the attention kernels meet keys that are complete: nothing of a line is shared with its value
         else:
             L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache,
                               q=qk, q_heads=H)
         opts = dict(vdim=dv if self.own_v else 0, chunk=self.chunk, sink=self.sink)
+        if self.talk is not None:
+            opts["key_heads"] = G
         if self.tc_rq:
             tile_rows, n_tiles = e.window_tiles(self.tc_rq)
             # few tiles (decoding): several CTAs share a tile's pages.  The share count depends on the tiling only (not on
@@ -433,7 +510,7 @@ class WindowAttentionMixer:
                                   self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, e.window_partial(d) if n_splits > 1 else None,
                                   **opts)
         else:
-            L.window_attention(qk, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
+            L.window_attention(q_in, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
                                self.cache, **opts)
         if self.w_g is not None:
             og = e.buf("og", H * dv)
@@ -500,13 +577,18 @@ class RoutedExperts:
             two largest scores, only the `keep` best groups are eligible;  "softmax": scores softmax(z) over all experts;
       renorm: the chosen scores are divided by their sum (+ 1e-20); router.scale then multiplies the weights;
       gated:  an expert is W_down (a sigma(1.702 a) (1 + b)), a = min(gate . h, limit), b = clamp(up . h, +-limit);
-              otherwise W_down relu(W_up h)^2.
-    The `top` best eligible experts run and their outputs are summed with the weights."""
+              "silu": W_down (silu(gate . h) (up . h));  otherwise W_down relu(W_up h)^2;
+      bias:   <prefix>router.b [experts] is added to the router logits;
+      shared: an mlp entry `shared: {ff}` brings one more gated expert <prefix>shared.gate / up / down that every token runs;
+              its output is multiplied by sigmoid(<prefix>shared.sg . h), one number per token, and added.
+    The `top` best eligible experts run and their outputs are summed with the weights.  Softmax scores divided by the sum
+    of the chosen ones are the softmax over the chosen logits alone."""
 
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng = eng
         tr = eng.cfg.traits.get("moe") or {}
         self.softmax, self.renorm, self.gated = tr.get("score", "sigmoid") == "softmax", bool(tr.get("renorm")), bool(tr.get("gated"))
+        self.gate_silu = tr.get("gated") == "silu"
         r = m["router"]
         self.E, self.top, self.ff = int(r["experts"]), int(r["top"]), int(m["expert"]["ff"])
         self.route_scale = float(r.get("scale") or 0.0)
@@ -515,7 +597,27 @@ class RoutedExperts:
         self.groups, self.keep = int(g["count"]), int(g["keep"])
         if self.E % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.keep * (self.E // self.groups):
             raise ValueError(f"layer {index}: {self.E} experts, {self.groups} groups (keep {self.keep}), top {self.top}")
-        self.router = eng.dense_weight(eng.weight(prefix + "router"))
+        wr = eng.weight(prefix + "router")
+        if tuple(wr.shape) != (self.E, eng.cfg.width):
+            raise ValueError(f"layer {index}: router has shape {tuple(wr.shape)}")
+        self.router_b = eng.vector(prefix + "router.b") if tr.get("bias") else None
+        if self.router_b is not None and tuple(self.router_b.shape) != (self.E,):
+            raise ValueError(f"layer {index}: router.b has shape {tuple(self.router_b.shape)}")
+        # a shared expert: its gate's row rides behind the router's rows (one product gives the logits and the gate);
+        # gate and up rows interleaved in one matrix (gate_0, up_0, gate_1, ...): the tensor-core product forms
+        # silu(gate) * up in its epilogue, the weight-streaming one reads the two strided halves
+        sh = m.get("shared") if tr.get("shared") else None
+        self.shared_ff = int(sh["ff"]) if sh else 0
+        self.w_sgu = self.w_sdown = None
+        if sh:
+            wsg, sg_, su_, sd_ = (eng.weight(prefix + "shared." + n) for n in ("sg", "gate", "up", "down"))
+            W_, F_ = eng.cfg.width, self.shared_ff
+            if tuple(wsg.shape) != (1, W_) or tuple(sg_.shape) != (F_, W_) or tuple(su_.shape) != (F_, W_) or tuple(sd_.shape) != (W_, F_):
+                raise ValueError(f"layer {index}: shared expert has shapes {tuple(wsg.shape)} / {tuple(sg_.shape)} / {tuple(su_.shape)} / {tuple(sd_.shape)}")
+            wr = torch.cat([wr, wsg], 0).contiguous()
+            self.w_sgu = eng.dense_weight(torch.stack([sg_, su_], dim=1).reshape(2 * F_, W_).contiguous())
+            self.w_sdown = eng.dense_weight(sd_)
+        self.router = eng.dense_weight(wr)
         self.w_up = torch.stack([eng.weight(f"{prefix}e{n}.up") for n in range(self.E)]).contiguous()        # [E][ff][W]
         self.w_down = torch.stack([eng.weight(f"{prefix}e{n}.down") for n in range(self.E)]).contiguous()    # [E][W][ff]
         self.w_gate = torch.stack([eng.weight(f"{prefix}e{n}.gate") for n in range(self.E)]).contiguous() if self.gated else None
@@ -524,26 +626,42 @@ class RoutedExperts:
             raise ValueError(f"layer {index}: expert weights have shapes {tuple(self.w_up.shape)} / {tuple(self.w_down.shape)}")
         # bf16 mode: batches of TC_MIN_ROWS rows and more sort their (row, expert) pairs by expert and run all experts as
         # one grouped tensor-core GEMM per projection; fewer rows stream the chosen experts' weights pair by pair
-        self.grouped = eng.L.MoeGrouped(self.w_up, self.w_down, self.top, eng.max_rows, w_gate=self.w_gate, limit=self.limit) if eng.tc else None
+        self.grouped = eng.L.MoeGrouped(self.w_up, self.w_down, self.top, eng.max_rows, w_gate=self.w_gate, limit=self.limit,
+                                        gate_silu=self.gate_silu) if eng.tc else None
 
     def scratch(self) -> Dict[str, int]:
-        return {"router_z": self.E, "moe_act": self.top * self.ff, "moe_sel": self.top, "moe_wgt": self.top}
+        n = {"router_z": self.router.N, "moe_act": self.top * self.ff, "moe_sel": self.top, "moe_wgt": self.top}
+        if self.shared_ff:
+            n["sh_g"], n["sh_a"] = self.shared_ff, self.shared_ff
+        return n
 
     def weight_bytes(self) -> int:
         n = self.w_up.numel() + self.w_down.numel() + (self.w_gate.numel() if self.gated else 0)
-        return self.router.nbytes() + n * self.w_up.element_size()
+        sh = self.w_sgu.nbytes() + self.w_sdown.nbytes() if self.shared_ff else 0
+        return self.router.nbytes() + n * self.w_up.element_size() + sh
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
         e, L = self.eng, self.eng.L
-        z, act = e.buf("router_z", self.E), e.buf("moe_act", self.top * self.ff)
+        z, act = e.buf("router_z", self.router.N), e.buf("moe_act", self.top * self.ff)
         sel, wgt = e.buf("moe_sel", self.top).view(torch.int32), e.buf("moe_wgt", self.top)
         e.mm(self.router, h, z, M, src="h")
         L.moe_select(z, M, self.E, self.top, self.groups, self.keep, sel, wgt, renorm=self.renorm, softmax=self.softmax,
-                     scale=self.route_scale)
+                     scale=self.route_scale, bias=self.router_b)
         if self.grouped is not None and M >= TC_MIN_ROWS:
             self.grouped.run(h, M, sel, wgt, y)
         else:
-            L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x, w_gate=self.w_gate, limit=self.limit)
+            L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x, w_gate=self.w_gate, limit=self.limit,
+                       gate_silu=self.gate_silu)
+        if self.shared_ff:          # y += sigmoid(z[:, E]) * W_down (silu(W_gate h) * (W_up h))
+            F = self.shared_ff
+            sh_a = e.buf("sh_a", F)
+            if self.w_sgu.wh is not None and M >= TC_MIN_ROWS:
+                e.mm(self.w_sgu, h, sh_a, M, epi=L.DENSE_GLU_SILU, src="h")
+            else:
+                sh_g, gu = e.buf("sh_g", F), self.w_sgu.t
+                L.dense(gu[0::2], h, sh_g, M, e.round_x, epi=L.DENSE_SILU)
+                L.dense(gu[1::2], h, sh_a, M, e.round_x, epi=L.DENSE_MUL, aux=sh_g)
+            e.mm(self.w_sdown, sh_a, y, M, epi=L.DENSE_ROWGATE_ADD, aux=z[:, self.E:])
 
 
 MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer, "attention": WindowAttentionMixer,
@@ -570,7 +688,7 @@ class _Layer:
         p = f"l{i}."
         if spec.type not in MIXERS:
             raise ValueError(f"layer {i}: unknown mixer type {spec.type!r}")
-        sandwich = eng.cfg.residual == "sandwich"
+        sandwich, post = eng.cfg.residual == "sandwich", eng.cfg.residual == "post"
         taps = eng.cfg.canon_taps
         # the last taps - 1 inputs of the convolution in front of the mixer: every layer's own, per sequence slot
         self.canon_state = torch.zeros(eng.n_slots, max(taps - 1, 1), eng.cfg.width, dtype=torch.float32, device=eng.device) if taps > 0 else None
@@ -584,7 +702,9 @@ class _Layer:
                 setattr(self, n, getattr(owner, n, None))
             return
         self.mixer = MIXERS[spec.type](eng, i, spec.mixer, p + "mix.")
-        self.norm1 = eng.norm_weight(p + "norm1")
+        # "post": the norm on a sublayer's output carries the residual multiplier, x <- x + (m g) * y / rms(y)
+        norm_w = (lambda name: (eng.norm_weight(name) * eng.cfg.residual_mult).contiguous()) if post else eng.norm_weight
+        self.norm1 = norm_w(p + "norm1")
         self.canon1 = None
         if taps > 0:
             self.canon1 = eng.weight(p + "canon1")
@@ -600,7 +720,7 @@ class _Layer:
             if kind not in FEED_FORWARDS:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
             self.ff = FEED_FORWARDS[kind](eng, i, spec.mlp, p + "mlp.")
-            self.norm2 = eng.norm_weight(p + "norm2")
+            self.norm2 = norm_w(p + "norm2")
             self.norm2b = eng.vector(p + "norm2b") if sandwich else None
             if not sandwich:
                 self.hc2 = _HyperWeights(eng, p + "hc2." if eng.cfg.hyper_weights else None)
@@ -691,7 +811,9 @@ class LayerListEngine:
         if lt and R >= LIGHTNING_CHUNKED_MIN_ROWS and os.environ.get("DLLAMA_LAYERS_CHUNKED_SCAN", "1") != "0":
             self._lightning_scratch = torch.zeros(max(L.lightning_chunk_floats(R, self.n_slots, mx.H, mx.dim, mx.vdim) for mx in lt),
                                                   dtype=torch.float32, device=dev)
-        if self.cfg.canon_taps and self.cfg.residual == "sandwich":
+        if self.cfg.residual == "post" and self.cfg.streams != 1:
+            raise ValueError("the post-norm residual style keeps one residual stream")
+        if self.cfg.canon_taps and self.cfg.residual != "hyper":
             raise ValueError("a convolution in front of the mixers is only wired into the pre-norm / hyper residual style")
         # scratch: one f32 buffer per name, as wide as the widest user
         widths: Dict[str, int] = {}
@@ -786,18 +908,18 @@ class LayerListEngine:
         return DenseWeight(t, self.tc)
 
     def mm(self, w: DenseWeight, x: torch.Tensor, y: torch.Tensor, M: int, epi: int = 0, aux=None, param: float = 0.0,
-           src: str = "tmp"):
+           src: str = "tmp", param2: float = 0.0):
         """y[:M] = epi(x[:M] @ w^T).  src="h": x is the current sublayer input; its tensor-core image is made by the
         first product that reads it (begin_sublayer() marks it stale) and shared by the others."""
         L = self.L
         if w.wh is None or M < TC_MIN_ROWS:
-            L.dense(w.t, x, y, M, self.round_x, epi=epi, aux=aux, param=param)
+            L.dense(w.t, x, y, M, self.round_x, epi=epi, aux=aux, param=param, param2=param2)
             return
         xh = self._xh[src]
         if src != "h" or not self._xh_h_ready:
             L.xh_from_rows(x, M, w.K, self.ncap, xh)
             self._xh_h_ready = src == "h" or self._xh_h_ready
-        L.dense_tc(w.wh, w.N, w.K, xh, self.ncap, y, M, epi=epi, aux=aux, param=param)
+        L.dense_tc(w.wh, w.N, w.K, xh, self.ncap, y, M, epi=epi, aux=aux, param=param, param2=param2)
 
     def mm_heads(self, w: DenseWeight, x: torch.Tensor, y: torch.Tensor, M: int, x_head_stride: int, y_head_stride: int):
         """Per head h: y[:M, h*ys : h*ys+N] = x[:M, h*xs : h*xs+K] @ w[h]^T."""
@@ -956,6 +1078,20 @@ class LayerListEngine:
             self._launch_hyper_layers(M)
             if n_logits:      # the copies summed, the model's norm, only the wanted rows
                 L.hyper_step(x, n_logits, cfg.streams, W, h=hn, norm_w=self.final_norm, eps=eps, rows=self.logit_rows)
+        elif cfg.residual == "post":
+            # every sublayer reads the stream itself; the norm of its output, times the multiplier, is summed into the stream
+            for l in self.layers:
+                self.begin_sublayer()
+                l.mixer.forward(x, y, M)
+                L.rms_norm(y, x, M, W, eps, w=l.norm1, accumulate=True)
+                if l.ff is not None:
+                    self.begin_sublayer()
+                    l.ff.forward(x, y, M)
+                    L.rms_norm(y, x, M, W, eps, w=l.norm2, accumulate=True)
+                if self.layer_probe is not None:
+                    self.layer_probe.append(x[:M].clone())
+            if n_logits:
+                L.rms_norm(x, hn, n_logits, W, eps, w=self.final_norm, rows=self.logit_rows)
         else:
             for l in self.layers:
                 L.rms_norm(x, hn, M, W, eps, w=l.norm1, plus_one=True)
@@ -1094,10 +1230,10 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
 
     sandwich = RESIDUAL_STYLES.get(config["architecture"], "sandwich") == "sandwich"
     traits = DESIGNS.get(config["architecture"], {})
-    att, moe = traits.get("attention") or {}, traits.get("moe") or {}
+    att, moe, lat = traits.get("attention") or {}, traits.get("moe") or {}, traits.get("latent") or {}
     taps = int((config.get("canon") or {}).get("taps") or 0)
     S = int(config.get("streams") or 0)
-    scalar_norms = config["architecture"] == "Venadra"          # one number per norm
+    scalar_norms = config["architecture"] == "Venadra" or traits.get("norm_weights") == "scalar"          # one number per norm
 
     def norm_w():
         if scalar_norms:
@@ -1130,7 +1266,9 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             if "kv_from" not in m:
                 t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = mat(r + dr, W), 1 + small(r)
             t[p + "mix.uk"], t[p + "mix.uv"] = mat(H * dn, r, 2.0), mat(H * dv, r)
-            t[p + "mix.g"], t[p + "mix.o"] = mat(H * dv, W), mat(W, H * dv)
+            t[p + "mix.g"], t[p + "mix.o"] = mat(H if lat.get("gate") == "head" else H * dv, W), mat(W, H * dv)
+            if lat.get("sink"):
+                t[p + "mix.sink"] = (torch.randn(H, generator=g)).to(torch.bfloat16)
         elif l["type"] == "mamba2":
             H, P, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
             inner, ch = H * P, H * P + 2 * G * N
@@ -1142,9 +1280,14 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             t[p + "mix.o"] = mat(W, inner)
         elif l["type"] == "attention":
             H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
-            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.o"] = mat(H * d, W, 2.0), mat(G * d, W, 2.0), mat(W, H * dv)
-            if att.get("values") == "own":
+            t[p + "mix.q"] = mat(H * d, W, 2.0)
+            if m.get("kv_from") is None:
+                t[p + "mix.k"] = mat(G * d, W, 2.0)
+            t[p + "mix.o"] = mat(W, H * dv)
+            if m.get("kv_from") is None and att.get("values") == "own":
                 t[p + "mix.v"] = mat(G * dv, W)
+            if att.get("talk"):     # near the identity, with cross-talk between all heads
+                t[p + "mix.talk"] = (torch.eye(H) + torch.randn(H, H, generator=g) * 0.3).to(torch.bfloat16)
             if att.get("sink"):
                 t[p + "mix.sink"] = (torch.randn(H, generator=g)).to(torch.bfloat16)
             if att.get("gate"):
@@ -1164,6 +1307,12 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             if (l["mlp"].get("kind") or ("moe" if "router" in l["mlp"] else "dense")) == "moe":
                 E, ff = l["mlp"]["router"]["experts"], l["mlp"]["expert"]["ff"]
                 t[p + "mlp.router"] = mat(E, W, 2.0)
+                if moe.get("bias"):
+                    t[p + "mlp.router.b"] = (torch.randn(E, generator=g) * 0.5).to(torch.bfloat16)
+                sh = l["mlp"].get("shared") if moe.get("shared") else None
+                if sh:
+                    t[p + "mlp.shared.gate"], t[p + "mlp.shared.up"] = mat(sh["ff"], W, 1.5), mat(sh["ff"], W, 1.5)
+                    t[p + "mlp.shared.down"], t[p + "mlp.shared.sg"] = mat(W, sh["ff"]), mat(1, W, 2.0)
                 for n in range(E):
                     t[p + f"mlp.e{n}.up"], t[p + f"mlp.e{n}.down"] = mat(ff, W, 1.5), mat(W, ff)
                     if moe.get("gated"):
@@ -1172,6 +1321,8 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
                 t[p + "mlp.up"], t[p + "mlp.down"] = mat(l["mlp"]["ff"], W), mat(W, l["mlp"]["ff"])
                 if traits.get("dense_act") == "polynorm":
                     t[p + "mlp.act"] = torch.tensor([0.6, 0.3, 0.15, 0.05]).add(torch.randn(4, generator=g) * 0.05).to(torch.bfloat16)
+                elif traits.get("dense_act") == "xielu":
+                    t[p + "mlp.act"] = (torch.randn(2, generator=g) * 0.5).to(torch.bfloat16)
     return t
 
 
@@ -1234,3 +1385,18 @@ def example_config_venadra(width: int = 160, vocab: int = 320, heads: int = 3, c
               {"type": "attention", "mixer": dict(attn), "mlp": dict(moe), "weights_of": 1}]
     return {"architecture": "Venadra", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 4.0},
             "canon": {"taps": 3}, "layers": layers}
+
+
+def example_config_darusun(width: int = 160, vocab: int = 320, heads: int = 6, kv_heads: int = 3, window: int = 40) -> dict:
+    """A small Darusun-shaped configuration: post-norm layers; grouped-query attention with rotate-half rotary, unit
+    queries and keys, head-mixed scores and values wider than the keys (one layer reads the first layer's keys and
+    values); a latent-attention layer with a sliding window, sinks and a gate per head; an xIELU feed-forward and routed
+    experts with a router bias and a shared expert."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": 32, "vdim": 48, "scale": 0.2, "rot": {"base": 10000.0, "dims": 16}}
+    lat = {"heads": 4, "dim": 24, "rot_dim": 8, "vdim": 32, "q_rank": 40, "kv_rank": 48, "scale": 1.0 / math.sqrt(32.0),
+           "rot": {"base": 10000.0, "dims": 8}, "mask": {"size": window}}
+    moe = {"kind": "moe", "expert": {"ff": 48}, "router": {"experts": 6, "top": 2}, "shared": {"ff": 80}}
+    layers = [{"type": "attention", "mixer": dict(attn), "mlp": {"kind": "dense", "ff": 2 * width}},
+              {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(moe)},
+              {"type": "attention", "mixer": dict(attn, kv_from=0), "mlp": dict(moe)}]
+    return {"architecture": "Darusun", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "layers": layers}

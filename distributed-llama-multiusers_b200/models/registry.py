@@ -21,6 +21,7 @@ ARCHITECTURES: Dict[str, Callable] = {
     "Ribivik": _layer_list,        # mamba2 and latent_attention mixers in the order its configuration lists
     "Sunesun": _layer_list,        # windowed attention (values = keys) + routed experts on hyper-connected residual streams
     "Venadra": _layer_list,        # lightning (linear) attention and chunked sink attention behind a short convolution, PolyNorm / gated experts
+    "Darusun": _layer_list,        # post-norm layers: head-mixed grouped-query attention, windowed latent attention with sinks, xIELU / experts with a shared one
 }
 
 

@@ -10,7 +10,8 @@ from typing import Optional
 import torch
 
 from . import lib
-from .lib import (DENSE_GLU_CLAMP, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SILU, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32,  # noqa: F401
+from .lib import (DENSE_GLU_CLAMP, DENSE_GLU_SILU, DENSE_MUL, DENSE_RELU2, DENSE_ROWGATE_ADD, DENSE_SIGMOID_MUL, DENSE_SILU, DENSE_SOFTCAP, DENSE_STORE,  # noqa: F401
+                  DENSE_XIELU, EPI_DENSE, T_BF16, T_F32,
                   DlConvArgs, DlDenseArgs, DlEpilogue, DlHyperArgs, DlLatentAttnArgs, DlLightningArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlMoeArgs,
                   DlMoePlanArgs, DlMoeSelectArgs, DlNormArgs, DlWindowAttnArgs, DlWindowKvArgs, check_layers, layers_lib)
 
@@ -46,7 +47,7 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, M: in
 
 
 def dense(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor, M: int, round_x: bool, epi: int = DENSE_STORE,
-          aux: Optional[torch.Tensor] = None, param: float = 0.0):
+          aux: Optional[torch.Tensor] = None, param: float = 0.0, param2: float = 0.0):
     """y[:M] = epi(x[:M] @ w^T); w [N][K] (rows may be strided), x [.., >= K] and y [.., >= N] row-major f32."""
     N, K = w.shape
     a = DlDenseArgs()
@@ -56,7 +57,7 @@ def dense(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor, M: int, round_x: bo
     a.M, a.N, a.K, a.batch = M, N, K, 1
     a.round_x, a.epi = 1 if round_x else 0, epi
     a.aux, a.ld_aux, a.aux_bs = _p(aux), (aux.stride(0) if aux is not None else 0), 0
-    a.param = param
+    a.param, a.param2 = param, param2
     check_layers(layers_lib().dl_dense(a, _stream()), "dl_dense")
     lib.count_launch()
 
@@ -71,7 +72,7 @@ def dense_heads(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor, M: int, round
     a.Y, a.ldy, a.y_bs = y.data_ptr(), y.stride(0), y_head_stride
     a.M, a.N, a.K, a.batch = M, N, K, H
     a.round_x, a.epi = 1 if round_x else 0, DENSE_STORE
-    a.aux, a.ld_aux, a.aux_bs, a.param = None, 0, 0, 0.0
+    a.aux, a.ld_aux, a.aux_bs, a.param, a.param2 = None, 0, 0, 0.0, 0.0
     check_layers(layers_lib().dl_dense(a, _stream()), "dl_dense")
     lib.count_launch()
 
@@ -103,12 +104,12 @@ def xh_from_rows(x: torch.Tensor, M: int, K: int, ncap: int, xh: torch.Tensor):
 
 
 def dense_tc(wh: torch.Tensor, N: int, K: int, xh: torch.Tensor, ncap: int, y: torch.Tensor, M: int, epi: int = DENSE_STORE,
-             aux: Optional[torch.Tensor] = None, param: float = 0.0):
+             aux: Optional[torch.Tensor] = None, param: float = 0.0, param2: float = 0.0):
     """y[:M, :N] = epi(x @ w^T) from the two operand images (bf16 x bf16 -> f32 in tensor memory)."""
     e = DlEpilogue()
     e.kind, e.n_dst, e.ld, e.dst_off = EPI_DENSE, 1, y.stride(0), 0
     e.dst[0] = y.data_ptr()
-    e.dense_op, e.dense_param = epi, param
+    e.dense_op, e.dense_param, e.dense_param2 = epi, param, param2
     e.dense_aux, e.dense_aux_ld = _p(aux), (aux.stride(0) if aux is not None else 0)
     check_layers(layers_lib().dl_gemm_wh_tc(wh.data_ptr(), N, _round_up(K, 128), xh.data_ptr(), ncap, M, e, 2, 0, _stream()),
                  "dl_gemm_wh_tc")
@@ -137,8 +138,9 @@ def poly_norm(x: torch.Tensor, y: torch.Tensor, M: int, dim: int, coef: torch.Te
 
 
 def latent_kv_write(kv: torch.Tensor, M: int, norm_w: torch.Tensor, eps: float, rank: int, rot: int, rope_dims: int,
-                    freqs: torch.Tensor, pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
+                    freqs: torch.Tensor, pos, slot, block_table: torch.Tensor, cache: torch.Tensor, interleaved: bool = False):
     a = DlLatentKvArgs()
+    a.interleaved = 1 if interleaved else 0
     a.kv, a.ld, a.norm_w, a.eps = kv.data_ptr(), kv.stride(0), norm_w.data_ptr(), eps
     a.rank, a.rot, a.rope_dims, a.freqs = rank, rot, rope_dims, freqs.data_ptr()
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
@@ -171,9 +173,12 @@ def latent_tc_partial_floats(n_tiles: int, n_splits: int, rank: int) -> int:
 
 def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_head_stride: int, q_rot_offset: int, out: torch.Tensor,
                      M: int, n_heads: int, rank: int, rot: int, scale: float, pos, slot, block_table: torch.Tensor,
-                     cache: torch.Tensor, tiles=None):
+                     cache: torch.Tensor, tiles=None, window: int = 0, sink: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None):
     """tiles = (tile_rows int32 [n_tiles][rq], n_tiles, rq, n_splits, partial f32 or None): the tensor-core kernel over
-    row tiles of one sequence each (bf16 cache); None: the per-row kernel (any cache type)."""
+    row tiles of one sequence each (bf16 cache); None: the per-row kernel (any cache type).  window > 0: a position sees
+    itself and the window - 1 before it; sink [heads]: joins the softmax denominator; gate [M][>= heads]: head h of row m
+    leaves multiplied by sigmoid(gate[m][h])."""
     a = DlLatentAttnArgs()
     a.q_lat, a.q, a.ldq = q_lat.data_ptr(), q.data_ptr(), q.stride(0)
     a.q_head_stride, a.q_rot_offset, a.out = q_head_stride, q_rot_offset, out.data_ptr()
@@ -181,6 +186,7 @@ def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_head_stride: int, q
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
     a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
     a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    a.window, a.sink, a.gate, a.ld_gate = window, _p(sink), _p(gate), (gate.stride(0) if gate is not None else 0)
     if tiles is not None:
         t = DlLatentTiles()
         t.tile_rows, t.n_tiles, t.rq, t.n_splits, t.partial = tiles[0].data_ptr(), tiles[1], tiles[2], tiles[3], _p(tiles[4])
@@ -296,14 +302,16 @@ def hyper_step(x: torch.Tensor, M: int, streams: int, dim: int, y: Optional[torc
 
 
 # ---- sliding-window attention whose values are its keys ---------------------------------------------------------------
-def window_kv_write(k: torch.Tensor, M: int, kv_heads: int, dim: int, rope_dims: int, freqs: torch.Tensor, rope_scale: float,
+def window_kv_write(k: Optional[torch.Tensor], M: int, kv_heads: int, dim: int, rope_dims: int, freqs: torch.Tensor, rope_scale: float,
                     pos, slot, block_table: torch.Tensor, cache: torch.Tensor, q: Optional[torch.Tensor] = None, q_heads: int = 0,
-                    v: Optional[torch.Tensor] = None, vdim: int = 0, qk_norm: bool = False, eps: float = 0.0):
+                    v: Optional[torch.Tensor] = None, vdim: int = 0, qk_norm: bool = False, eps: float = 0.0, rope_half: bool = False,
+                    talk: Optional[torch.Tensor] = None, q_mixed: Optional[torch.Tensor] = None):
     """Keys into the paged cache (rotated key + unrotated head per line); with q [M][q_heads * dim] the queries are
-    rotated in place by the same launch.  With v [M][kv_heads * vdim] (no rotary) the line is key + value, and qk_norm
-    divides every query and key head by its root mean square first."""
+    rotated in place by the same launch.  With v [M][kv_heads * vdim] the line is key + value; rotary (pairs (i, i + dims / 2)
+    with rope_half, else (2i, 2i + 1)) comes first, then qk_norm divides every query and key head by its root mean square.
+    talk [q_heads][q_heads] f32 with q_mixed [M][q_heads * kv_heads * dim]: the head mix of the scores, folded into the queries."""
     a = DlWindowKvArgs()
-    a.k, a.ld, a.kv_heads, a.dim, a.rope_dims = k.data_ptr(), k.stride(0), kv_heads, dim, rope_dims
+    a.k, a.ld, a.kv_heads, a.dim, a.rope_dims = _p(k), (k.stride(0) if k is not None else 0), kv_heads, dim, rope_dims
     a.q, a.ldq, a.q_heads = _p(q), (q.stride(0) if q is not None else 0), q_heads
     a.freqs, a.rope_scale = freqs.data_ptr(), rope_scale
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
@@ -311,12 +319,13 @@ def window_kv_write(k: torch.Tensor, M: int, kv_heads: int, dim: int, rope_dims:
     a.cache, a.ctype = cache.data_ptr(), _type(cache)
     a.v, a.ldv, a.vdim = _p(v), (v.stride(0) if v is not None else 0), vdim
     a.qk_norm, a.eps = 1 if qk_norm else 0, eps
+    a.rope_half, a.talk, a.q_mixed, a.ld_qm = 1 if rope_half else 0, _p(talk), _p(q_mixed), (q_mixed.stride(0) if q_mixed is not None else 0)
     check_layers(layers_lib().dl_window_kv_write(a, M, _stream()), "dl_window_kv_write")
     lib.count_launch()
 
 
 def _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache,
-                 vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None):
+                 vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None, key_heads: int = 0):
     a = DlWindowAttnArgs()
     a.q, a.ldq, a.out, a.ldo = q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0)
     a.heads, a.kv_heads, a.dim, a.rope_dims = heads, kv_heads, dim, rope_dims
@@ -324,16 +333,17 @@ def _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
     a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
     a.cache, a.ctype = cache.data_ptr(), _type(cache)
-    a.vdim, a.chunk, a.sink = vdim, chunk, _p(sink)
+    a.vdim, a.chunk, a.sink, a.key_heads = vdim, chunk, _p(sink), key_heads
     return a
 
 
 def window_attention(q: torch.Tensor, out: torch.Tensor, M: int, heads: int, kv_heads: int, dim: int, rope_dims: int,
                      scale: float, softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor,
-                     vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None):
+                     vdim: int = 0, chunk: int = 0, sink: Optional[torch.Tensor] = None, key_heads: int = 0):
     """The per-row kernel (either cache type, f32 arithmetic).  vdim > 0: values of their own behind the keys; chunk > 0:
-    only keys of the row's own chunk of positions are visible; sink [heads]: joins the softmax denominator."""
-    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, vdim, chunk, sink)
+    only keys of the row's own chunk of positions are visible; sink [heads]: joins the softmax denominator; key_heads =
+    kv_heads: q is [M][heads][kv_heads * dim] (head-mixed queries) against the keys of all key/value heads side by side."""
+    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, vdim, chunk, sink, key_heads)
     check_layers(layers_lib().dl_window_attention(a, M, _stream()), "dl_window_attention")
     lib.count_launch()
 
@@ -382,19 +392,20 @@ def window_attention_tiles(q, out, heads, kv_heads, dim, rope_dims, scale, softc
 
 # ---- routed experts ---------------------------------------------------------------------------------------------------
 def moe_select(z: torch.Tensor, M: int, experts: int, top: int, groups: int, keep: int, sel: torch.Tensor, wgt: torch.Tensor,
-               group_top: int = 2, renorm: bool = False, softmax: bool = False, scale: float = 0.0):
+               group_top: int = 2, renorm: bool = False, softmax: bool = False, scale: float = 0.0, bias: Optional[torch.Tensor] = None):
     """sel / wgt [M][top]: the chosen experts and their weights.  Scores: sigmoid(z), or softmax(z) over all experts;
     renorm divides the chosen scores by their sum (+ 1e-20); scale (0: none) multiplies the weights."""
     a = DlMoeSelectArgs()
     a.z, a.ldz, a.M, a.experts, a.top, a.groups, a.keep = z.data_ptr(), z.stride(0), M, experts, top, groups, keep
     a.group_top, a.renorm, a.sel, a.wgt = group_top, 1 if renorm else 0, sel.data_ptr(), wgt.data_ptr()
-    a.score, a.scale = 1 if softmax else 0, scale
+    a.score, a.scale, a.bias = 1 if softmax else 0, scale, _p(bias)
     check_layers(layers_lib().dl_moe_select(a, _stream()), "dl_moe_select")
     lib.count_launch()
 
 
 def moe_rows(w_up: torch.Tensor, w_down: torch.Tensor, x: torch.Tensor, M: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
-             act: torch.Tensor, y: torch.Tensor, round_x: bool, w_gate: Optional[torch.Tensor] = None, limit: float = 0.0):
+             act: torch.Tensor, y: torch.Tensor, round_x: bool, w_gate: Optional[torch.Tensor] = None, limit: float = 0.0,
+             gate_silu: bool = False):
     """w_up [experts][ff][width], w_down [experts][width][ff]; one product per (row, chosen expert) pair.  With w_gate
     (like w_up) the experts are gated: a sigma(1.702 a) (1 + b) on the products a, b clamped by `limit`, else relu(u)^2."""
     a = DlMoeArgs()
@@ -402,7 +413,7 @@ def moe_rows(w_up: torch.Tensor, w_down: torch.Tensor, x: torch.Tensor, M: int, 
     a.width, a.ff, a.top, a.M, a.round_x = w_up.shape[2], w_up.shape[1], top, M, 1 if round_x else 0
     a.x, a.ldx, a.sel, a.wgt = x.data_ptr(), x.stride(0), sel.data_ptr(), wgt.data_ptr()
     a.act, a.y, a.ldy = act.data_ptr(), y.data_ptr(), y.stride(0)
-    a.w_gate, a.limit = _p(w_gate), limit
+    a.w_gate, a.limit, a.gate_act = _p(w_gate), limit, 1 if gate_silu else 0
     check_layers(layers_lib().dl_moe_rows(a, _stream()), "dl_moe_rows")
     lib.count_launch(2)
 
@@ -413,13 +424,14 @@ class MoeGrouped:
     -> weighted combine.  Nothing returns to the host between the launches."""
 
     def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, top: int, max_rows: int, w_gate: Optional[torch.Tensor] = None,
-                 limit: float = 0.0):
+                 limit: float = 0.0, gate_silu: bool = False):
         Lb = layers_lib()
         self.E, self.ff, self.width, self.top = w_up.shape[0], w_up.shape[1], w_up.shape[2], top
         dev = w_up.device
         # gated experts: gate and up rows interleaved (gate_0, up_0, gate_1, ...) in ONE image of 2 ff rows, so the first
         # grouped GEMM's epilogue sees a value's two products side by side and stores the activation
         self.gated, self.limit = w_gate is not None, limit
+        self.glu_op = DENSE_GLU_SILU if gate_silu else DENSE_GLU_CLAMP
         self.n_up = self.ff
         if self.gated:
             w_up = torch.stack([w_gate, w_up], dim=2).reshape(self.E, 2 * self.ff, self.width).contiguous()
@@ -450,7 +462,7 @@ class MoeGrouped:
         e = DlEpilogue()
         e.kind, e.n_dst, e.ld, e.dst_off = EPI_DENSE, 1, y.stride(0), 0
         e.dst[0] = y.data_ptr()
-        e.dense_op, e.dense_param, e.dense_aux, e.dense_aux_ld = epi, param, None, 0
+        e.dense_op, e.dense_param, e.dense_param2, e.dense_aux, e.dense_aux_ld = epi, param, 0.0, None, 0
         check_layers(layers_lib().dl_gemm_wh_tc_grouped(wh.data_ptr(), group_bytes, self.E, self.grp.data_ptr(), N, _round_up(K, 128),
                                                         xh.data_ptr(), self.cap, M, e, 2, _stream()), "dl_gemm_wh_tc_grouped")
         lib.count_launch()
@@ -467,7 +479,7 @@ class MoeGrouped:
         check_layers(Lb.dl_xh_gather_rows(x.data_ptr(), x.stride(0), self.slot_row.data_ptr(), n_sorted, self.width, self.cap,
                                           self.xh_in.data_ptr(), _stream()), "dl_xh_gather_rows")
         if self.gated:
-            self._gemm(self.wh_up, self.up_bytes, self.n_up, self.width, self.xh_in, self.act, M, DENSE_GLU_CLAMP, self.limit)
+            self._gemm(self.wh_up, self.up_bytes, self.n_up, self.width, self.xh_in, self.act, M, self.glu_op, self.limit)
         else:
             self._gemm(self.wh_up, self.up_bytes, self.ff, self.width, self.xh_in, self.act, M, DENSE_RELU2)
         check_layers(Lb.dl_xh_from_rows(self.act.data_ptr(), self.act.stride(0), n_sorted, self.ff, self.cap, self.xh_act.data_ptr(),

@@ -60,6 +60,7 @@ class DlEpilogue(C.Structure):
         ("dense_param", C.c_float),
         ("dense_aux", C.c_void_p),
         ("dense_aux_ld", C.c_longlong),
+        ("dense_param2", C.c_float),
     ]
 
 
@@ -214,6 +215,7 @@ def check(rc: int, what: str = ""):
 # ---- hyper-connections, routed experts)
 T_F32, T_BF16 = 0, 1
 DENSE_STORE, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_SILU, DENSE_GLU_CLAMP = 0, 1, 2, 3, 4, 5
+DENSE_MUL, DENSE_XIELU, DENSE_ROWGATE_ADD, DENSE_GLU_SILU = 6, 7, 8, 9
 
 
 class DlDenseArgs(C.Structure):
@@ -224,7 +226,7 @@ class DlDenseArgs(C.Structure):
                 ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("batch", C.c_int),
                 ("round_x", C.c_int), ("epi", C.c_int),
                 ("aux", C.c_void_p), ("ld_aux", C.c_longlong), ("aux_bs", C.c_longlong),
-                ("param", C.c_float)]
+                ("param", C.c_float), ("param2", C.c_float)]
 
 
 class DlNormArgs(C.Structure):
@@ -240,7 +242,8 @@ class DlLatentKvArgs(C.Structure):
     _fields_ = [("kv", C.c_void_p), ("ld", C.c_longlong), ("norm_w", C.c_void_p), ("eps", C.c_float),
                 ("rank", C.c_int), ("rot", C.c_int), ("rope_dims", C.c_int), ("freqs", C.c_void_p),
                 ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
-                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
+                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int),
+                ("interleaved", C.c_int)]
 
 
 class DlLatentAttnArgs(C.Structure):
@@ -249,7 +252,8 @@ class DlLatentAttnArgs(C.Structure):
                 ("q_rot_offset", C.c_int), ("out", C.c_void_p), ("n_heads", C.c_int), ("rank", C.c_int),
                 ("rot", C.c_int), ("scale", C.c_float), ("pos", C.c_void_p), ("slot", C.c_void_p),
                 ("block_table", C.c_void_p), ("max_pages", C.c_int), ("page_size", C.c_int),
-                ("cache", C.c_void_p), ("ctype", C.c_int)]
+                ("cache", C.c_void_p), ("ctype", C.c_int),
+                ("window", C.c_int), ("sink", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_longlong)]
 
 
 class DlLatentTiles(C.Structure):
@@ -293,7 +297,8 @@ class DlWindowKvArgs(C.Structure):
                 ("freqs", C.c_void_p), ("rope_scale", C.c_float),
                 ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
                 ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int),
-                ("v", C.c_void_p), ("ldv", C.c_longlong), ("vdim", C.c_int), ("qk_norm", C.c_int), ("eps", C.c_float)]
+                ("v", C.c_void_p), ("ldv", C.c_longlong), ("vdim", C.c_int), ("qk_norm", C.c_int), ("eps", C.c_float),
+                ("rope_half", C.c_int), ("talk", C.c_void_p), ("q_mixed", C.c_void_p), ("ld_qm", C.c_longlong)]
 
 
 class DlWindowAttnArgs(C.Structure):
@@ -303,7 +308,7 @@ class DlWindowAttnArgs(C.Structure):
                 ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
                 ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
                 ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int),
-                ("vdim", C.c_int), ("chunk", C.c_int), ("sink", C.c_void_p)]
+                ("vdim", C.c_int), ("chunk", C.c_int), ("sink", C.c_void_p), ("key_heads", C.c_int)]
 
 
 class DlConvArgs(C.Structure):
@@ -326,7 +331,8 @@ class DlMoeSelectArgs(C.Structure):
     """Mirror of ``DlMoeSelectArgs``."""
     _fields_ = [("z", C.c_void_p), ("ldz", C.c_longlong), ("M", C.c_int), ("experts", C.c_int), ("top", C.c_int),
                 ("groups", C.c_int), ("keep", C.c_int), ("group_top", C.c_int), ("renorm", C.c_int),
-                ("sel", C.c_void_p), ("wgt", C.c_void_p), ("score", C.c_int), ("scale", C.c_float)]
+                ("sel", C.c_void_p), ("wgt", C.c_void_p), ("score", C.c_int), ("scale", C.c_float),
+                ("bias", C.c_void_p)]
 
 
 class DlMoeArgs(C.Structure):
@@ -334,7 +340,8 @@ class DlMoeArgs(C.Structure):
     _fields_ = [("w_up", C.c_void_p), ("w_down", C.c_void_p), ("wtype", C.c_int),
                 ("width", C.c_int), ("ff", C.c_int), ("top", C.c_int), ("M", C.c_int), ("round_x", C.c_int),
                 ("x", C.c_void_p), ("ldx", C.c_longlong), ("sel", C.c_void_p), ("wgt", C.c_void_p),
-                ("act", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong), ("w_gate", C.c_void_p), ("limit", C.c_float)]
+                ("act", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong), ("w_gate", C.c_void_p), ("limit", C.c_float),
+                ("gate_act", C.c_int)]
 
 
 class DlMoePlanArgs(C.Structure):

@@ -25,7 +25,11 @@ enum {
 };
 /* element-wise ops on a matmul result (dense-weight models): store, relu(.)^2, aux * sigmoid(.), param * tanh(. / param) */
 enum { DL_DENSE_STORE = 0, DL_DENSE_RELU2 = 1, DL_DENSE_SIGMOID_MUL = 2, DL_DENSE_SOFTCAP = 3, DL_DENSE_SILU = 4,
-       DL_DENSE_GLU_CLAMP = 5 /* tensor-core epilogue only: output columns (2j, 2j+1) = (gate, up) of value j, see DlMoeArgs */ };
+       DL_DENSE_GLU_CLAMP = 5 /* tensor-core epilogue only: output columns (2j, 2j+1) = (gate, up) of value j, see DlMoeArgs */,
+       DL_DENSE_MUL = 6          /* aux[m][n] * (.)                                                                  */,
+       DL_DENSE_XIELU = 7        /* z > 0: param z^2 + z / 2;  else: param2 (exp(z) - 1 - z) + z / 2                 */,
+       DL_DENSE_ROWGATE_ADD = 8  /* y[m][n] + sigmoid(aux[m * ld_aux]) * (.): one gate per row, added to what y holds */,
+       DL_DENSE_GLU_SILU = 9     /* tensor-core epilogue only, columns paired like GLU_CLAMP: silu(gate) * up        */ };
 
 typedef struct {
     int kind;
@@ -66,6 +70,7 @@ typedef struct {
     float dense_param;
     const float* dense_aux;
     long long dense_aux_ld;
+    float dense_param2;
 } DlEpilogue;
 
 /* Fused activation producer for dl_gemv_q40: the kernel itself computes
@@ -313,7 +318,9 @@ int dl_peer_barrier(uint32_t* const* flags_on_peers /*host array*/, uint32_t* my
 
 /* Y[b][m][n] = epi( sum_k X[b][m][k] * W[b][n][k] ),  b < batch (element strides *_bs).  round_x: the activation
  * operand is rounded to bf16 on load (bf16 mode).  DL_DENSE_SIGMOID_MUL: aux[m][n] * sigmoid(.);
- * DL_DENSE_SOFTCAP: param * tanh(. / param); DL_DENSE_SILU: . * sigmoid(.). */
+ * DL_DENSE_SOFTCAP: param * tanh(. / param); DL_DENSE_SILU: . * sigmoid(.); DL_DENSE_MUL: aux[m][n] * (.);
+ * DL_DENSE_XIELU: param z^2 + z / 2 for z > 0, else param2 (exp(z) - 1 - z) + z / 2;
+ * DL_DENSE_ROWGATE_ADD: Y[m][n] + sigmoid(aux[m * ld_aux]) * (.) (Y is read, then written). */
 typedef struct {
     const void* W; int wtype; long long ldw, w_bs;
     const float* X; long long ldx, x_bs;
@@ -323,6 +330,7 @@ typedef struct {
     int epi;
     const float* aux; long long ld_aux, aux_bs;
     float param;
+    float param2;
 } DlDenseArgs;
 int dl_dense(const DlDenseArgs* args /*host*/, void* stream);
 /* x[m][c][dim] = scale * table[tokens[m]] for c < copies */
@@ -364,6 +372,7 @@ typedef struct {
     const int* pos; const int* slot; const int* block_table;
     int max_pages, page_size;
     void* cache; int ctype;
+    int interleaved;                          /* rotary pairs: 0: dimension i with i + rope_dims / 2, 1: 2i with 2i + 1 */
 } DlLatentKvArgs;
 int dl_latent_kv_write(const DlLatentKvArgs* args /*host*/, int M, void* stream);
 /* rotary on dims [offset, offset + rope_dims) of every head of x, in place.  interleaved: dimension 2i pairs with 2i + 1
@@ -383,6 +392,9 @@ typedef struct {
     const int* pos; const int* slot; const int* block_table;
     int max_pages, page_size;
     const void* cache; int ctype;
+    int window;                               /* > 0: only the positions j with pos[m] - j < window are visible */
+    const float* sink;                        /* [n_heads] or NULL: exp(sink[h]) joins the softmax denominator, without a value */
+    const float* gate; long long ld_gate;     /* NULL, or [M][ld_gate]: head h of row m leaves multiplied by sigmoid(gate[m][h]) */
 } DlLatentAttnArgs;
 int dl_latent_attention(const DlLatentAttnArgs* args /*host*/, int M, void* stream);
 /* Tensor-core variant (bf16 cache).  The batch's rows are grouped on the host into tiles of up to `rq` rows of one
@@ -491,9 +503,18 @@ typedef struct {
     const int* pos; const int* slot; const int* block_table;
     int max_pages, page_size;
     void* cache; int ctype;
-    /* separate values (v != NULL): the line is [ key[0 : dim] | value[0 : vdim] ], no rotary (rope_dims 0) */
+    /* separate values (vdim > 0): the line is [ key[0 : dim] | value[0 : vdim] ].  k and v both NULL: only the queries are
+     * prepared (a layer that reads the cache another layer writes) */
     const float* v; long long ldv; int vdim;
     int qk_norm; float eps;                   /* every query and key head h becomes h / sqrt(mean(h^2) + eps) */
+    /* separate values with rotary (rope_dims > 0): the first rope_dims dimensions of every query and key head are turned
+     * BEFORE the unit norm; rope_half 1: dimension i pairs with i + rope_dims / 2, 0: 2i with 2i + 1 */
+    int rope_half;
+    /* head-mixed scores ("talking heads" in front of the softmax): talk [q_heads][q_heads] f32.  Since
+     * score'_h = sum_g talk[h][g] q_g . k_c(g) = sum_c (sum_{g in group c} talk[h][g] q_g) . k_c, the mix is folded into the
+     * queries: q_mixed[m][h][c * dim + i] = sum_{g in group c} talk[h][g] q[m][g][i] (after rotary and norm), a query of
+     * kv_heads * dim numbers per head that meets the concatenated keys of all key/value heads (DlWindowAttnArgs.key_heads) */
+    const float* talk; float* q_mixed; long long ld_qm;
 } DlWindowKvArgs;
 int dl_window_kv_write(const DlWindowKvArgs* args /*host*/, int M, void* stream);
 /* out[m][h] = sum_j softmax_j(cap(scale q[m][h] . key_j)) value_j over the positions j with 0 <= pos[m] - j < window
@@ -510,6 +531,9 @@ typedef struct {
     int vdim;                                 /* > 0: separate values, line [ key | value[0 : vdim] ], out [M][heads * vdim] */
     int chunk;                                /* > 0: j is visible only inside i's chunk, floor(j / chunk) == floor(i / chunk) */
     const float* sink;                        /* [heads] or NULL: exp(sink[h]) joins the softmax denominator, without a value */
+    int key_heads;                            /* 0 / 1: a head's key is its key/value head's; kv_heads: q is [M][heads][kv_heads * dim] and
+                                                 meets the keys of ALL key/value heads side by side (head-mixed scores, see DlWindowKvArgs.talk);
+                                                 the values stay those of the head's own key/value head */
 } DlWindowAttnArgs;
 int dl_window_attention(const DlWindowAttnArgs* args /*host*/, int M, void* stream);
 
@@ -524,6 +548,7 @@ typedef struct {
     int score;                                /* 0: s = sigmoid(z); 1: s = softmax(z) over all experts */
     float scale;                              /* 0 / 1: none; else the weights are multiplied by it (after renorm, whose
                                                  divisor is the sum of the chosen scores + 1e-20) */
+    const float* bias;                        /* [experts] or NULL: added to z before the scores */
 } DlMoeSelectArgs;
 int dl_moe_select(const DlMoeSelectArgs* args /*host*/, void* stream);
 /* y[m] = sum_k wgt[m][k] * W_down[e] relu(W_up[e] x[m])^2, e = sel[m][k]; w_up [experts][ff][width], w_down
@@ -538,6 +563,7 @@ typedef struct {
     /* w_gate != NULL: gated experts, [experts][ff][width] like w_up:  a = min(gate . x, limit), b = clamp(up . x, +-limit),
      * hidden = a * sigma(1.702 a) * (1 + b)  (limit <= 0: no clamps) */
     const void* w_gate; float limit;
+    int gate_act;                             /* gated experts, 1: hidden = silu(gate . x) * (up . x), no clamps */
 } DlMoeArgs;
 int dl_moe_rows(const DlMoeArgs* args /*host*/, void* stream);
 /* Grouped form for the tensor cores.  dl_moe_plan sorts the M * top (row, expert) pairs by expert (stable) into segments
