@@ -63,7 +63,7 @@ def _run(cmd, verbose, log_path=None):
 
 # sources of the layer-list model library; prep.cu (error plumbing, argmax), sampler.cu and gemm_wh_tc.cu (the tcgen05
 # GEMM on pre-tiled operands) are shared with the other one (their objects are compiled once), the rest is its own
-LAYERS_OWN = ["dense.cu", "hyper.cu", "latent_attention.cu", "lightning.cu", "mamba2.cu", "moe.cu", "norms.cu", "window_attention.cu"]
+LAYERS_OWN = ["dense.cu", "hyper.cu", "latent_attention.cu", "lightning.cu", "mamba2.cu", "moe.cu", "norms.cu", "talk_attention.cu", "window_attention.cu"]
 LAYERS_SHARED = ["gemm_wh_tc.cu", "prep.cu", "sampler.cu"]
 
 

@@ -1,0 +1,333 @@
+// Grouped-query attention on the tensor cores whose values have a width of their own and whose scores may be mixed
+// across heads before the softmax ("talking heads"):
+//     s_g(i, j)  = scale * q_g,i . k_c(g),j                       c(g) = g / (heads / kv_heads)
+//     s'_h(i, j) = sum_g talk[h][g] s_g(i, j)                     then mask, softmax, sink as in window_attention.cu
+//     out_h(i)   = sum_j p_h(i, j) v_c(h),j
+// The mix is linear in the queries, so the cache writer (attn_kv_write_kernel) folds it into them:
+//     s'_h(i, j) = scale * sum_c Q_h,i[c] . k_c,j,     Q_h,i[c] = sum_{g: c(g) = c} talk[h][g] q_g,i
+// -- head h carries ONE query of key_heads * dim numbers that meets the keys of ALL key/value heads side by side, and
+// the kernel is an ordinary attention tile kernel whose K dimension is key_heads * dim: nothing is exchanged between
+// heads here.  key_heads <= 1 is plain grouped-query attention (the query meets its own group's key only).
+//
+// Cache [page][kv_head][32][dim + vdim] bf16, one line = key | value.  A CTA owns a tile of up to `rq` consecutive
+// positions of one sequence and the query heads of ONE key/value head g: (position, head-of-the-group) pairs stack on the
+// M dimension, 4 warps x 16 stacked rows.  Per page of 32 tokens it stages the keys of every key/value head and the values
+// of head g (cp.async, two buffers: page k + 1 is in flight while page k is multiplied), then per warp
+//     S[16 x 32]  = Q[16 x KH * DP] . K[32 x KH * DP]^T      Q (bf16, staged once per tile) and K by ldmatrix
+//     scale, mask, online softmax in f32 and base 2
+//     O[16 x DVP] += P[16 x 32] . V[32 x DVP]                  P from the score registers, V by ldmatrix.trans
+// mma.sync m16n8k16 bf16, f32 accumulators.  DP / DVP: dim / vdim rounded up to the template's sizes, the padding kept at
+// zero in shared memory.  Few tiles (decoding): n_splits CTAs share a tile's pages and talk_merge_kernel combines them.
+#include "mma_common.cuh"
+#include "../../../include/dllama_b200.h"
+
+#define TA_PAGE 32
+#define TA_ROWS 64
+#define TA_MAX_SPLITS 32
+#define TA_LOG2E 1.4426950408889634f
+#define TA_LN2 0.6931471805599453f
+
+__device__ __forceinline__ float ta_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__host__ __device__ __forceinline__ int ta_stride(int n) {      // bf16 elements; rows 16 B apart modulo 128 B
+    int s = (n + 7) / 8 * 8 + 8;
+    if ((s * 2) % 128 == 0) s += 8;
+    return s;
+}
+
+template <int DK, int NV>
+__global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
+                                                                float* __restrict__ partial) {
+    constexpr int DP = 16 * DK, DVP = 8 * NV;
+    extern __shared__ __align__(16) uint8_t smraw[];
+    __shared__ int s_row[TA_ROWS];
+    const int D = a.dim, DV = a.vdim, LD = D + DV;
+    const int KH = a.key_heads > 1 ? a.key_heads : 1, QD = KH * D, QDP = KH * DP;
+    const int LDS = ta_stride(QDP + DVP), QS = ta_stride(QDP);
+    __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][TA_PAGE][LDS]: keys of all heads | values of head g
+    __nv_bfloat16* q_s = kv_s + (size_t)2 * TA_PAGE * LDS;                          // [TA_ROWS][QS]: the stacked queries
+    const int tile = blockIdx.x, g = blockIdx.y, rep = a.heads / a.kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    if (threadIdx.x < rq) s_row[threadIdx.x] = tile_rows[(size_t)tile * rq + threadIdx.x];
+    // the padding of keys and values stays zero: the copies below never touch it
+    for (int i = threadIdx.x; i < 2 * TA_PAGE * LDS / 8; i += 128) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    int n_rows = 0;
+    while (n_rows < rq && s_row[n_rows] >= 0) ++n_rows;
+    if (n_rows == 0) return;
+    const int p_first = a.pos[s_row[0]], p_last = p_first + n_rows - 1, slot = a.slot[s_row[0]];
+    int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    if (a.chunk > 0) lo = max(lo, p_first / a.chunk * a.chunk);
+    int pg_lo = lo / TA_PAGE, pg_hi = p_last / TA_PAGE;
+    if (n_splits > 1) {                  // this CTA's share of the tile's pages (possibly none)
+        const int per = (pg_hi - pg_lo + n_splits) / n_splits;
+        pg_lo += (int)blockIdx.z * per;
+        pg_hi = min(pg_hi, pg_lo + per - 1);
+    }
+    const bool active = warp * 16 < n_rows * rep;
+    const float c1 = a.scale * TA_LOG2E;
+
+    // this thread's two stacked rows: s = position-in-tile * rep + head-in-group
+    const int s0 = warp * 16 + gid, s1 = s0 + 8;
+    const int r0 = s0 / rep, r1 = s1 / rep;
+    const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
+    const int pos0 = p_first + r0, pos1 = p_first + r1;
+    const int cs0 = a.chunk > 0 ? pos0 / a.chunk * a.chunk : 0, cs1 = a.chunk > 0 ? pos1 / a.chunk * a.chunk : 0;
+    const int cs_last = a.chunk > 0 ? p_last / a.chunk * a.chunk : 0;
+    // the tile's queries, rounded to bf16, zero-padded per key head
+    for (int idx = threadIdx.x; idx < TA_ROWS * (QDP / 4); idx += 128) {
+        const int sr = idx / (QDP / 4), col = (idx - sr * (QDP / 4)) * 4;
+        const int c = col / DP, d = col - c * DP, r = sr / rep;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < n_rows && d < D) v = *reinterpret_cast<const float4*>(a.q + (size_t)s_row[r] * a.ldq + (size_t)(g * rep + sr % rep) * QD + c * D + d);
+        uint2 pk;
+        pk.x = pack_bf16(v.x, v.y);
+        pk.y = pack_bf16(v.z, v.w);
+        *reinterpret_cast<uint2*>(q_s + (size_t)sr * QS + col) = pk;
+    }
+    float o[NV][4];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) { o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int kch = D / 8, vch = DV / 8, per_line = KH * kch + vch;
+    auto issue = [&](int pg, int buf) {
+        const int page = a.block_table[(size_t)slot * a.max_pages + pg];
+        const __nv_bfloat16* src0 = (const __nv_bfloat16*)a.cache + (size_t)page * a.kv_heads * TA_PAGE * LD;
+        __nv_bfloat16* dst = kv_s + (size_t)buf * TA_PAGE * LDS;
+        for (int i = threadIdx.x; i < TA_PAGE * per_line; i += 128) {
+            const int j = i / per_line, part = i - j * per_line;
+            if (part < KH * kch) {
+                const int c = part / kch, p = part - c * kch;
+                cp_async16(dst + (size_t)j * LDS + c * DP + p * 8, src0 + ((size_t)(KH > 1 ? c : g) * TA_PAGE + j) * LD + p * 8);
+            } else {
+                const int p = part - KH * kch;
+                cp_async16(dst + (size_t)j * LDS + QDP + p * 8, src0 + ((size_t)g * TA_PAGE + j) * LD + D + p * 8);
+            }
+        }
+    };
+    if (pg_lo <= pg_hi) issue(pg_lo, 0);
+    const int mat = lane >> 3, rr = lane & 7;
+    for (int pg = pg_lo; pg <= pg_hi; ++pg) {
+        const int buf = (pg - pg_lo) & 1;
+        cp_async_wait_all();
+        __syncthreads();                      // page pg has landed (and the queries); everyone is done with the other buffer
+        if (pg < pg_hi) issue(pg + 1, buf ^ 1);
+        if (!active) continue;
+        const __nv_bfloat16* kv = kv_s + (size_t)buf * TA_PAGE * LDS;
+        float sc[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+        for (int c = 0; c < KH; ++c) {
+#pragma unroll
+            for (int kk = 0; kk < DK; ++kk) {
+                uint32_t qf[4];
+                ldmatrix_x4(qf, q_s + (size_t)(warp * 16 + (mat & 1) * 8 + rr) * QS + c * DP + kk * 16 + (mat >> 1) * 8);
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, kv + (size_t)(np * 16 + (mat >> 1) * 8 + rr) * LDS + c * DP + kk * 16 + (mat & 1) * 8);
+                    mma_bf16(sc[2 * np], qf, b[0], b[1]);
+                    mma_bf16(sc[2 * np + 1], qf, b[2], b[3]);
+                }
+            }
+        }
+        // scale (base-2 scores) and mask (skipped on pages that every row of the tile sees whole)
+        const int pg_first = pg * TA_PAGE;
+        const bool whole = pg_first + TA_PAGE - 1 <= p_first && (a.window == 0 || p_last - pg_first < a.window) && pg_first >= cs_last;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float s2 = sc[n][e] * c1;
+                if (!whole) {
+                    const int j = pg_first + n * 8 + tig * 2 + (e & 1);
+                    const int pr = (e < 2) ? pos0 : pos1;
+                    const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window) && j >= ((e < 2) ? cs0 : cs1);
+                    s2 = vis ? s2 : -INFINITY;
+                }
+                sc[n][e] = s2;
+                if (e < 2) mx0 = fmaxf(mx0, s2); else mx1 = fmaxf(mx1, s2);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float al0 = (m0 == -INFINITY) ? 0.f : ta_ex2(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : ta_ex2(m1 - mn1);
+        const float ref0 = (mn0 == -INFINITY) ? 0.f : mn0, ref1 = (mn1 == -INFINITY) ? 0.f : mn1;      // a row that sees nothing yet: every p = 0
+        m0 = mn0; m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            sc[n][0] = ta_ex2(sc[n][0] - ref0); sc[n][1] = ta_ex2(sc[n][1] - ref0);
+            sc[n][2] = ta_ex2(sc[n][2] - ref1); sc[n][3] = ta_ex2(sc[n][3] - ref1);
+            ps0 += sc[n][0] + sc[n][1];
+            ps1 += sc[n][2] + sc[n][3];
+        }
+        l0 = l0 * al0 + ps0;
+        l1 = l1 * al1 + ps1;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { o[v][0] *= al0; o[v][1] *= al0; o[v][2] *= al1; o[v][3] *= al1; }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+            pa[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
+            pa[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+            pa[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+            for (int vp = 0; vp < NV / 2; ++vp) {
+                const int vt = 2 * vp + (mat >> 1);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, kv + (size_t)(ks * 16 + (mat & 1) * 8 + rr) * LDS + QDP + vt * 8);
+                mma_bf16(o[2 * vp], pa, b[0], b[1]);
+                mma_bf16(o[2 * vp + 1], pa, b[2], b[3]);
+            }
+        }
+    }
+    if (!active) return;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (n_splits > 1) {                  // unnormalised sums, running maximum and sum per stacked row, for the merge kernel
+        float* base = partial + (((size_t)tile * a.kv_heads + g) * n_splits + blockIdx.z) * TA_ROWS * (DVP + 2);
+        if (ok0) {
+            float* dst = base + (size_t)s0 * (DVP + 2);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][0], o[v][1]);
+            if (tig == 0) { dst[DVP] = m0 * TA_LN2; dst[DVP + 1] = l0; }
+        }
+        if (ok1) {
+            float* dst = base + (size_t)s1 * (DVP + 2);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][2], o[v][3]);
+            if (tig == 0) { dst[DVP] = m1 * TA_LN2; dst[DVP + 1] = l1; }
+        }
+        return;
+    }
+    if (a.sink) {                        // the sink's share of the denominator, in the base-2 scale of the running maximum
+        if (ok0) l0 += ta_ex2(a.sink[g * rep + s0 % rep] * TA_LOG2E - m0);
+        if (ok1) l1 += ta_ex2(a.sink[g * rep + s1 % rep] * TA_LOG2E - m1);
+    }
+    if (ok0) {
+        float* dst = a.out + (size_t)s_row[r0] * a.ldo + (size_t)(g * rep + s0 % rep) * DV;
+        const float inv = 1.f / l0;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+            if (v * 8 < DV) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][0] * inv, o[v][1] * inv);
+    }
+    if (ok1) {
+        float* dst = a.out + (size_t)s_row[r1] * a.ldo + (size_t)(g * rep + s1 % rep) * DV;
+        const float inv = 1.f / l1;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+            if (v * 8 < DV) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][2] * inv, o[v][3] * inv);
+    }
+}
+
+// merge of the page shares: one CTA per (tile, key/value head, position of the tile).  The shares' maxima and sums are
+// gathered into shared memory, every (head, share) weight e^(m_k - m) / l is formed once, then a thread per (head,
+// column) sums the shares.
+__global__ void __launch_bounds__(128) talk_merge_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
+                                                         const float* __restrict__ partial, int DVP) {
+    __shared__ float w_s[TA_ROWS * TA_MAX_SPLITS], l_s[TA_ROWS * TA_MAX_SPLITS];
+    const int tile = blockIdx.x, g = blockIdx.y, r = blockIdx.z, DV = a.vdim, rep = a.heads / a.kv_heads;
+    const int m = tile_rows[(size_t)tile * rq + r];
+    if (m < 0) return;
+    const float* base = partial + ((size_t)tile * a.kv_heads + g) * n_splits * TA_ROWS * (DVP + 2);
+    for (int idx = threadIdx.x; idx < rep * n_splits; idx += blockDim.x) {
+        const int hg = idx / n_splits, k = idx - hg * n_splits;
+        const float* p = base + ((size_t)k * TA_ROWS + r * rep + hg) * (DVP + 2);
+        w_s[idx] = p[DVP];
+        l_s[idx] = p[DVP + 1];
+    }
+    __syncthreads();
+    for (int hg = threadIdx.x; hg < rep; hg += blockDim.x) {
+        float mx = -INFINITY, l = 0.f;
+        for (int k = 0; k < n_splits; ++k) mx = fmaxf(mx, w_s[hg * n_splits + k]);
+        for (int k = 0; k < n_splits; ++k) {
+            const float mk = w_s[hg * n_splits + k];
+            const float e = mk == -INFINITY ? 0.f : expf(mk - mx);
+            l += l_s[hg * n_splits + k] * e;
+            w_s[hg * n_splits + k] = e;
+        }
+        if (a.sink) l += expf(a.sink[g * rep + hg] - mx);
+        const float inv = 1.f / l;
+        for (int k = 0; k < n_splits; ++k) w_s[hg * n_splits + k] *= inv;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rep * DV; idx += blockDim.x) {
+        const int hg = idx / DV, c = idx - hg * DV;
+        const float* p = base + (size_t)(r * rep + hg) * (DVP + 2) + c;
+        float acc = 0.f;                      // a share without pages wrote nothing and weighs 0
+        for (int k = 0; k < n_splits; ++k) {
+            const float w = w_s[hg * n_splits + k];
+            if (w != 0.f) acc = fmaf(w, p[(size_t)k * TA_ROWS * (DVP + 2)], acc);
+        }
+        a.out[(size_t)m * a.ldo + (size_t)(g * rep + hg) * DV + c] = acc;
+    }
+}
+
+static int ta_dk(int dim) { return dim <= 32 ? 2 : dim <= 64 ? 4 : 8; }
+static int ta_nv(int vdim) { return vdim <= 32 ? 4 : vdim <= 64 ? 8 : vdim <= 96 ? 12 : 16; }
+static size_t ta_smem(int dim, int vdim, int key_heads) {
+    const int KH = key_heads > 1 ? key_heads : 1, QDP = KH * 16 * ta_dk(dim);
+    return ((size_t)2 * TA_PAGE * ta_stride(QDP + 8 * ta_nv(vdim)) + (size_t)TA_ROWS * ta_stride(QDP)) * sizeof(__nv_bfloat16);
+}
+
+// 0 if the kernel takes these sizes: a bf16 cache, dim and vdim multiples of 8 up to 128, at most 64 query heads per
+// key/value head, and a tile's queries plus two pages of all key heads within the shared memory of an SM
+extern "C" int dl_talk_attention_tc_supported(int heads, int kv_heads, int dim, int vdim, int key_heads, int ctype) {
+    if (ctype != DL_T_BF16 || heads < 1 || kv_heads < 1 || heads % kv_heads || heads / kv_heads > TA_ROWS) return -1;
+    if (dim < 8 || dim % 8 || dim > 128 || vdim < 8 || vdim % 8 || vdim > 128) return -1;
+    if (key_heads > 1 && key_heads != kv_heads) return -1;
+    if (ta_smem(dim, vdim, key_heads) > 200 * 1024) return -1;
+    return 0;
+}
+
+extern "C" long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int vdim) {
+    return (long long)n_tiles * kv_heads * n_splits * TA_ROWS * (8 * ta_nv(vdim) + 2);
+}
+
+template <int DK, int NV>
+static int launch_talk(const DlWindowAttnArgs& a, const int* tile_rows, int n_tiles, int rq, int n_splits, float* partial, size_t smem, cudaStream_t st) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<DK, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { dl_set_error("dl_talk_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
+    }
+    talk_attention_mma_kernel<DK, NV><<<dim3(n_tiles, a.kv_heads, n_splits), 128, smem, st>>>(a, tile_rows, rq, n_splits, partial);
+    return 0;
+}
+
+// tile_rows[n_tiles][rq] (device; -1 where a tile has fewer rows): up to rq = 64 / (heads / kv_heads) consecutive rows of
+// one sequence per tile.  q: [M][heads][max(key_heads, 1) * dim].  n_splits > 1: that many CTAs share each tile's pages
+// and leave partial sums in `partial` (dl_talk_tc_partial_floats() f32) that a merge launch combines.
+extern "C" int dl_talk_attention_tc(const DlWindowAttnArgs* args, const int* tile_rows, int n_tiles, int rq, int n_splits,
+                                    float* partial, void* stream) {
+    const DlWindowAttnArgs& a = *args;
+    if (a.page_size != TA_PAGE || a.softcap != 0.f || a.rope_dims != 0 || a.window < 0 || a.chunk < 0 ||
+        dl_talk_attention_tc_supported(a.heads, a.kv_heads, a.dim, a.vdim, a.key_heads, a.ctype) != 0 || rq < 1 ||
+        rq * (a.heads / a.kv_heads) > TA_ROWS || (a.ldq & 3) || (a.ldo & 1) || ((uintptr_t)a.q & 15) || ((uintptr_t)a.out & 7)) {
+        dl_set_error("dl_talk_attention_tc: sizes not supported (heads %d / %d, dim %d, vdim %d, key heads %d, rq %d)", a.heads, a.kv_heads, a.dim, a.vdim, a.key_heads, rq);
+        return -1;
+    }
+    if (n_tiles < 1) return 0;
+    if (n_splits < 1 || n_splits > TA_MAX_SPLITS || (n_splits > 1 && partial == nullptr)) { dl_set_error("dl_talk_attention_tc: n_splits %d without scratch", n_splits); return -1; }
+    const size_t smem = ta_smem(a.dim, a.vdim, a.key_heads);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int dk = ta_dk(a.dim), nv = ta_nv(a.vdim);
+    int rc = -1;
+#define TA_CASE(DK_, NV_) if (dk == DK_ && nv == NV_) rc = launch_talk<DK_, NV_>(a, tile_rows, n_tiles, rq, n_splits, partial, smem, st);
+    TA_CASE(2, 4) TA_CASE(2, 8) TA_CASE(2, 12) TA_CASE(2, 16)
+    TA_CASE(4, 4) TA_CASE(4, 8) TA_CASE(4, 12) TA_CASE(4, 16)
+    TA_CASE(8, 4) TA_CASE(8, 8) TA_CASE(8, 12) TA_CASE(8, 16)
+#undef TA_CASE
+    if (rc != 0) return rc;
+    if (n_splits > 1) talk_merge_kernel<<<dim3(n_tiles, a.kv_heads, rq), 128, 0, st>>>(a, tile_rows, rq, n_splits, partial, 8 * nv);
+    LAYER_CHECK_LAUNCH("dl_talk_attention_tc");
+    return 0;
+}

@@ -448,10 +448,15 @@ class WindowAttentionMixer:
         self.cache = torch.zeros(eng.n_pages, G, PAGE, self.line, dtype=eng.wdtype, device=eng.device) if self.kv_from is None else None
         # bf16 caches of sizes the tensor-core kernel takes: tiles of tc_rq consecutive rows of a sequence (0: per-row kernel)
         L = eng.L
-        self.tc_rq = 0
-        if eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0" and dv == d and self.talk is None and \
-                L.window_tc_supported(H, G, d, 0 if self.own_v else self.rope_dims, eng.wdtype):
+        self.tc_rq, self.tc_talk = 0, False
+        self.partial_width = d                  # columns of a page share's partial sums
+        attn_tc = eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0"
+        if attn_tc and dv == d and self.talk is None and L.window_tc_supported(H, G, d, 0 if self.own_v else self.rope_dims, eng.wdtype):
             self.tc_rq = L.window_tc_rows(H, G)
+        elif attn_tc and self.own_v and self.softcap == 0.0 and L.talk_tc_supported(H, G, d, dv, G if self.talk is not None else 0, eng.wdtype):
+            # values wider or narrower than the keys, head-mixed scores: the tile kernel of talk_attention.cu
+            self.tc_rq, self.tc_talk = L.window_tc_rows(H, G), True
+            self.partial_width = (dv + 31) // 32 * 32
 
     def scratch(self) -> Dict[str, int]:
         n = {"qk": (self.H + self.G) * self.dim + (self.G * self.vdim if self.own_v else 0), "o": self.H * self.vdim}
@@ -506,9 +511,13 @@ class WindowAttentionMixer:
             n_splits = 1
             if n_tiles * G <= 2 * e.n_sms:
                 n_splits = max(1, min(pages, WINDOW_MAX_SPLITS, (WINDOW_CTAS_PER_SM * e.n_sms) // (n_tiles * G)))
-            L.window_attention_tc(qk, o, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
-                                  self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, e.window_partial(d) if n_splits > 1 else None,
-                                  **opts)
+            partial = e.window_partial(self.partial_width) if n_splits > 1 else None
+            if self.tc_talk:
+                L.talk_attention_tc(q_in, o, H, G, d, dv, self.scale, self.window, e.pos, e.slot, e.block_table, self.cache, tile_rows,
+                                    n_tiles, self.tc_rq, n_splits, partial, chunk=self.chunk, sink=self.sink, key_heads=opts.get("key_heads", 0))
+            else:
+                L.window_attention_tc(qk, o, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
+                                      self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, partial, **opts)
         else:
             L.window_attention(q_in, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
                                self.cache, **opts)
@@ -846,7 +855,7 @@ class LayerListEngine:
         self._desc_len = self._chunks_off + 2 * self._max_chunks
         # then, per tile height rq of the windowed-attention layers, tile_rows [tiles][rq] of their tensor-core kernel
         self._window_partial = None
-        wd = [mx.dim for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq]
+        wd = [mx.partial_width for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq]
         if wd:
             self.window_partial(max(wd))               # allocated before any graph is captured
         self._wtile_off: Dict[int, int] = {}

@@ -314,7 +314,7 @@ int dl_peer_barrier(uint32_t* const* flags_on_peers /*host array*/, uint32_t* my
 
 /* ==== layer-list models: dense bf16 / f32 weights, latent attention, Mamba-2 ===================
  * Built into libdllama_b200_layers.so (dense.cu, norms.cu, latent_attention.cu, mamba2.cu, hyper.cu, window_attention.cu,
- * moe.cu, plus the shared prep.cu, sampler.cu and gemm_wh_tc.cu).  Activations between kernels are f32; `wtype` / `ctype`: 0 = f32, 1 = bf16. */
+ * talk_attention.cu, lightning.cu, moe.cu, plus the shared prep.cu, sampler.cu and gemm_wh_tc.cu).  Activations between kernels are f32; `wtype` / `ctype`: 0 = f32, 1 = bf16. */
 
 /* Y[b][m][n] = epi( sum_k X[b][m][k] * W[b][n][k] ),  b < batch (element strides *_bs).  round_x: the activation
  * operand is rounded to bf16 on load (bf16 mode).  DL_DENSE_SIGMOID_MUL: aux[m][n] * sigmoid(.);
@@ -591,6 +591,12 @@ int dl_window_attention_tc_supported(int heads, int kv_heads, int dim, int rope_
 long long dl_window_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int dim);
 int dl_window_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* tile_rows, int n_tiles, int rq, int n_splits,
                            float* partial, void* stream);
+/* The tile kernel for values of a width of their own (vdim > 0, any multiple of 8 up to 128; rope_dims 0, no soft cap) and
+ * for head-mixed scores (key_heads = kv_heads: q [M][heads][kv_heads * dim], talk_attention.cu).  Tiles as above. */
+int dl_talk_attention_tc_supported(int heads, int kv_heads, int dim, int vdim, int key_heads, int ctype);
+long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int vdim);
+int dl_talk_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* tile_rows, int n_tiles, int rq, int n_splits,
+                         float* partial, void* stream);
 
 #ifdef __cplusplus
 }
