@@ -51,11 +51,12 @@ def parse_args():
     ap.add_argument("--layered", default="", help="instead of the headline benchmark: prefill and decode throughput of the "
                     "layer-list design (Ribivik: Mamba-2 + latent attention, bf16) beside a Q40 Llama of equal width, "
                     "feed-forward size and depth, at these sizes (comma separated: w2048, w4096); prints one JSON line")
-    ap.add_argument("--layered-design", default="ribivik", choices=("ribivik", "sunesun", "venadra"),
+    ap.add_argument("--layered-design", default="ribivik", choices=("ribivik", "sunesun", "venadra", "darusun"),
                     help="--layered: which layer-list design runs beside the Llama arm (ribivik: Mamba-2 + latent attention; "
                          "sunesun: windowed attention whose values are its keys + routed experts on hyper-connected streams; "
-                         "venadra: lightning and chunked sink attention, PolyNorm and gated experts -- beside it also Sunesun, "
-                         "the closest layer-list design, at equal width, depth and experts)")
+                         "venadra: lightning and chunked sink attention, PolyNorm and gated experts; darusun: post-norm layers, "
+                         "head-mixed attention, windowed latent attention, xIELU and experts with a shared one -- beside these two "
+                         "also Sunesun, the closest layer-list design, at equal width, depth and experts)")
     ap.add_argument("--layered-layers", type=int, default=4, help="--layered: layers of both models")
     ap.add_argument("--layered-prompt", type=int, default=2048, help="--layered: prompt length (one batch)")
     return ap.parse_args()
@@ -466,6 +467,25 @@ def venadra_config(name: str, n_layers: int, vocab: int, chunk: int = 1024) -> d
             "canon": {"taps": 4}, "layers": layers}
 
 
+def darusun_config(name: str, n_layers: int, vocab: int, window: int = 1024) -> dict:
+    """Width, heads and experts of the Sunesun arm.  Layers in turn: head-mixed attention + dense xIELU, windowed latent
+    attention + experts, head-mixed attention on the first layer's keys and values + experts, head-mixed attention +
+    experts; four key/value heads, 64 rotated dimensions; a shared expert twice as wide as a routed one."""
+    import math
+    sz, ss = LAYERED_SIZES[name], SUNESUN_SIZES[name]
+    attn = {"heads": ss["heads"], "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 0.1, "rot": {"base": 500000.0, "dims": 64}}
+    lat = {"heads": sz["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": sz["q_rank"], "kv_rank": sz["kv_rank"],
+           "scale": 1.0 / math.sqrt(192.0), "rot": {"base": 10000.0, "dims": 64}, "mask": {"size": window}}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": ss["expert_ff"]}, "router": {"experts": ss["experts"], "top": ss["top"]},
+           "shared": {"ff": 2 * ss["expert_ff"]}}
+    layers = []
+    for i in range(n_layers):
+        mixer = dict(lat) if i % 4 == 1 else dict(attn, kv_from=0) if i % 4 == 2 else dict(attn)
+        layers.append({"type": "latent_attention" if i % 4 == 1 else "attention", "mixer": mixer, "mlp": dict(moe if i % 4 else dense)})
+    return {"architecture": "Darusun", "width": sz["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": layers}
+
+
 def _time_ms(fn, warmup: int, steps: int):
     import torch
     for _ in range(warmup):
@@ -534,7 +554,7 @@ def run_layered(args):
         sz = LAYERED_SIZES[name]
         design = args.layered_design
         configs = {"ribivik": lambda: layered_config(sz, nl, vocab), "sunesun": lambda: sunesun_config(name, nl, vocab),
-                   "venadra": lambda: venadra_config(name, nl, vocab)}
+                   "venadra": lambda: venadra_config(name, nl, vocab), "darusun": lambda: darusun_config(name, nl, vocab)}
 
         def layer_list_arm(dsg):
             d = os.path.join(args.model_dir, f"dllama_b200_{'layered' if dsg == 'ribivik' else dsg}_{name}_l{nl}")
@@ -549,7 +569,7 @@ def run_layered(args):
             return r
 
         r = layer_list_arm(design)
-        beside = {"sunesun_bf16": layer_list_arm("sunesun")} if design == "venadra" else {}
+        beside = {"sunesun_bf16": layer_list_arm("sunesun")} if design in ("venadra", "darusun") else {}
         shape = dict(dim=sz["width"], hidden_dim=sz["ff"], n_layers=nl, n_heads=sz["heads"], n_kv_heads=8, vocab_size=vocab,
                      max_seq_len=8192, rope_theta=10000, rope=None)
         path = os.path.join(args.model_dir, f"dllama_b200_llama_{name}_l{nl}_q40.m")

@@ -34,7 +34,7 @@ def steps(a):
     d = os.path.join(a.model_dir, f"dllama_b200_{'layered' if a.design == 'ribivik' else a.design}_{a.size}_l{nl}")
     if not os.path.exists(os.path.join(d, "model.safetensors")):
         cfg = {"ribivik": lambda: bench.layered_config(bench.LAYERED_SIZES[a.size], nl, vocab), "sunesun": lambda: bench.sunesun_config(a.size, nl, vocab),
-               "venadra": lambda: bench.venadra_config(a.size, nl, vocab)}[a.design]()
+               "venadra": lambda: bench.venadra_config(a.size, nl, vocab), "darusun": lambda: bench.darusun_config(a.size, nl, vocab)}[a.design]()
         write_random_model(d, cfg, seed=1)
     torch.cuda.set_device(0)
     eng = registry.engine_for_dir(d, max_rows=T, n_slots=users, max_seq_len=T + 64, dtype="bfloat16")
@@ -116,7 +116,7 @@ def lightning_scan(a):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=("steps", "window-attention", "lightning-scan"))
-    ap.add_argument("--design", default="sunesun", choices=("ribivik", "sunesun", "venadra"))
+    ap.add_argument("--design", default="sunesun", choices=("ribivik", "sunesun", "venadra", "darusun"))
     ap.add_argument("--size", default="w2048")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=2048)

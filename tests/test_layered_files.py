@@ -1,6 +1,7 @@
 """Model directories without a GPU: the safetensors container, the configuration reader, the architecture registry,
 the random-model writer, and the oracle's own consistency."""
 import json
+import math
 import os
 
 import pytest
@@ -154,3 +155,59 @@ def test_venadra_oracle_chunks_recurrence_and_prefix_property():
     o = V.decayed_linear_attention(q, k, v, 0.8)
     want = sum(0.8 ** (8 - j) * float(q[8] @ k[j]) * v[j] for j in range(9))
     assert torch.allclose(o[8], want, atol=1e-12)
+
+
+# ---- Darusun: configuration, design traits, weight names, the oracle's own window, head mix and routing -----------------------
+def test_darusun_configuration_traits_and_tensor_names(tmp_path):
+    from dllama_b200.models.layered import DESIGNS, example_config_darusun
+    cfg = example_config_darusun()
+    d = str(tmp_path / "d")
+    tensors = write_random_model(d, cfg, seed=1)
+    assert registry.architecture_of(d) == "Darusun" and "Darusun" in registry.ARCHITECTURES
+    c = LayerListConfig.load(d)
+    assert (c.residual, c.streams, c.residual_mult, c.canon_taps, c.embed_scale, c.logit_softcap) == ("post", 1, 0.6, 0, 1.0, 0.0)
+    assert c.traits is DESIGNS["Darusun"] and c.traits["attention"]["talk"] and c.traits["latent"]["gate"] == "head"
+    assert tensors["l0.norm1"].dim() == 0 and tensors["final.norm"].dim() == 0 and "l0.norm1b" not in tensors
+    assert tensors["l0.mix.talk"].shape == (6, 6) and tensors["l0.mix.v"].shape == (3 * 48, 160) and tensors["l0.mlp.act"].shape == (2,)
+    assert tensors["l1.mix.g"].shape == (4, 160) and tensors["l1.mix.sink"].shape == (4,) and tensors["l1.mix.dkv"].shape == (48 + 8, 160)
+    assert tensors["l1.mlp.router.b"].shape == (6,) and tensors["l1.mlp.shared.sg"].shape == (1, 160) and tensors["l1.mlp.e5.gate"].shape == (48, 160)
+    assert "l2.mix.k" not in tensors and "l2.mix.v" not in tensors and tensors["l2.mix.q"].shape == (6 * 32, 160)
+    # the same mixer types under another design keep that design's meaning: Ribivik's latent attention gates every column
+    assert random_tensors(example_config(blocks=1), seed=1)["l0.mix.g"].shape[0] == 4 * 24
+
+
+def test_darusun_oracle_window_head_mix_routing_and_prefix_property():
+    """The oracle itself: appended tokens change nothing before them; through windowed latent layers alone a changed token
+    reaches one window further per layer and no more; an identity head mix leaves plain attention; the folded form of the
+    mix equals the mix of the scores; the chosen experts' weights sum to one."""
+    import darusun_oracle as D
+    lat = {"heads": 2, "dim": 8, "rot_dim": 4, "vdim": 6, "q_rank": 10, "kv_rank": 12, "scale": 0.3, "rot": {"base": 100.0, "dims": 4}, "mask": {"size": 5}}
+    cfg = {"architecture": "Darusun", "width": 48, "vocab": 40, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+           "layers": [{"type": "latent_attention", "mixer": lat, "mlp": {"kind": "dense", "ff": 32}},
+                      {"type": "latent_attention", "mixer": lat, "mlp": {"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 4, "top": 2}, "shared": {"ff": 12}}}]}
+    t = random_tensors(cfg, seed=2)
+    toks = torch.randint(0, 40, (30,), generator=torch.Generator().manual_seed(3)).tolist()
+    a, b = D.model_logits(t, cfg, toks), D.model_logits(t, cfg, toks[:11])
+    assert torch.allclose(a[:11], b, atol=1e-9)
+    other = list(toks)
+    other[3] = (toks[3] + 1) % 40
+    c = D.model_logits(t, cfg, other)
+    # layer 0 carries position 3 to 3..7, layer 1 from there to 11 at most
+    assert torch.allclose(a[:3], c[:3], atol=1e-9) and not torch.allclose(a[11], c[11], atol=1e-9) and torch.allclose(a[12:], c[12:], atol=1e-9)
+    g = torch.Generator().manual_seed(5)
+    T, H, G, d, dv = 9, 4, 2, 6, 5
+    q, k, v = (torch.randn(T, n, m, generator=g, dtype=torch.float64) for n, m in ((H, d), (G, d), (G, dv)))
+    plain = D.mixed_head_softmax_rows(q, k, v, 0.7, torch.eye(H, dtype=torch.float64))
+    for h in range(H):
+        p = torch.softmax(0.7 * (k[:, h // 2] @ q[8, h]), -1)
+        assert torch.allclose(plain[8, h], p @ v[:, h // 2], atol=1e-12)
+    talk = torch.randn(H, H, generator=g, dtype=torch.float64)
+    mixed = D.mixed_head_softmax_rows(q, k, v, 0.7, talk)
+    folded_q = torch.stack([torch.cat([sum(talk[h, gg] * q[:, gg] for gg in range(c * 2, c * 2 + 2)) for c in range(G)], -1) for h in range(H)], 1)   # [T, H, G * d]
+    s = 0.7 * torch.einsum("hx,sx->hs", folded_q[8], k.reshape(T, G * d))
+    for h in range(H):
+        assert torch.allclose(mixed[8, h], torch.softmax(s[h], -1) @ v[:, h // 2], atol=1e-12)
+    z = torch.tensor([[0.1, 2.0, -1.0, 2.0, 0.5]], dtype=torch.float64)
+    sel, w = D.route(z, 3)
+    assert sel.tolist() == [[1, 3, 4]] and abs(float(w.sum()) - 1.0) < 1e-12 and abs(float(w[0, 0] / w[0, 2]) - math.exp(1.5)) < 1e-9
+    assert abs(float(D.xielu(torch.tensor([2.0], dtype=torch.float64), 0.0, 0.0)) - (math.log(2.0) * 4 + 1)) < 1e-12
