@@ -11,7 +11,9 @@
 //
 // Cache [page][kv_head][32][dim + vdim] bf16, one line = key | value.  A CTA owns a tile of up to `rq` consecutive
 // positions of one sequence and the query heads of ONE key/value head g: (position, head-of-the-group) pairs stack on the
-// M dimension, 4 warps x 16 stacked rows.  Per page of 32 tokens it stages the keys of every key/value head and the values
+// M dimension, NR warps x 16 stacked rows: NR = 8 (256 threads, 128 stacked rows) for long portions, where a staged page
+// serves twice the queries; 4 for medium ones; 1 for decoding (one warp multiplies, all four stage; the small query tile
+// lets two CTAs share an SM).  Per page of 32 tokens it stages the keys of every key/value head and the values
 // of head g (cp.async, two buffers: page k + 1 is in flight while page k is multiplied), then per warp
 //     S[16 x 32]  = Q[16 x KH * DP] . K[32 x KH * DP]^T      Q (bf16, staged once per tile) and K by ldmatrix
 //     scale, mask, online softmax in f32 and base 2
@@ -22,7 +24,7 @@
 #include "../../../include/dllama_b200.h"
 
 #define TA_PAGE 32
-#define TA_ROWS 64
+#define TA_MAX_ROWS 128
 #define TA_MAX_SPLITS 32
 #define TA_LOG2E 1.4426950408889634f
 #define TA_LN2 0.6931471805599453f
@@ -39,10 +41,10 @@ __host__ __device__ __forceinline__ int ta_stride(int n) {      // bf16 elements
     return s;
 }
 
-template <int DK, int NV>
-__global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
+template <int DK, int NV, int NR>
+__global__ void __launch_bounds__(NR == 8 ? 256 : 128) talk_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
                                                                 float* __restrict__ partial) {
-    constexpr int DP = 16 * DK, DVP = 8 * NV;
+    constexpr int DP = 16 * DK, DVP = 8 * NV, TA_ROWS = 16 * NR, THREADS = NR == 8 ? 256 : 128;
     extern __shared__ __align__(16) uint8_t smraw[];
     __shared__ int s_row[TA_ROWS];
     const int D = a.dim, DV = a.vdim, LD = D + DV;
@@ -54,7 +56,7 @@ __global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArg
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     if (threadIdx.x < rq) s_row[threadIdx.x] = tile_rows[(size_t)tile * rq + threadIdx.x];
     // the padding of keys and values stays zero: the copies below never touch it
-    for (int i = threadIdx.x; i < 2 * TA_PAGE * LDS / 8; i += 128) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < 2 * TA_PAGE * LDS / 8; i += THREADS) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     int n_rows = 0;
     while (n_rows < rq && s_row[n_rows] >= 0) ++n_rows;
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArg
         pg_lo += (int)blockIdx.z * per;
         pg_hi = min(pg_hi, pg_lo + per - 1);
     }
-    const bool active = warp * 16 < n_rows * rep;
+    const bool active = warp < NR && warp * 16 < n_rows * rep;
     const float c1 = a.scale * TA_LOG2E;
 
     // this thread's two stacked rows: s = position-in-tile * rep + head-in-group
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArg
     const int cs0 = a.chunk > 0 ? pos0 / a.chunk * a.chunk : 0, cs1 = a.chunk > 0 ? pos1 / a.chunk * a.chunk : 0;
     const int cs_last = a.chunk > 0 ? p_last / a.chunk * a.chunk : 0;
     // the tile's queries, rounded to bf16, zero-padded per key head
-    for (int idx = threadIdx.x; idx < TA_ROWS * (QDP / 4); idx += 128) {
+    for (int idx = threadIdx.x; idx < TA_ROWS * (QDP / 4); idx += THREADS) {
         const int sr = idx / (QDP / 4), col = (idx - sr * (QDP / 4)) * 4;
         const int c = col / DP, d = col - c * DP, r = sr / rep;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArg
         const int page = a.block_table[(size_t)slot * a.max_pages + pg];
         const __nv_bfloat16* src0 = (const __nv_bfloat16*)a.cache + (size_t)page * a.kv_heads * TA_PAGE * LD;
         __nv_bfloat16* dst = kv_s + (size_t)buf * TA_PAGE * LDS;
-        for (int i = threadIdx.x; i < TA_PAGE * per_line; i += 128) {
+        for (int i = threadIdx.x; i < TA_PAGE * per_line; i += THREADS) {
             const int j = i / per_line, part = i - j * per_line;
             if (part < KH * kch) {
                 const int c = part / kch, p = part - c * kch;
@@ -233,8 +235,8 @@ __global__ void __launch_bounds__(128) talk_attention_mma_kernel(DlWindowAttnArg
 // gathered into shared memory, every (head, share) weight e^(m_k - m) / l is formed once, then a thread per (head,
 // column) sums the shares.
 __global__ void __launch_bounds__(128) talk_merge_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
-                                                         const float* __restrict__ partial, int DVP) {
-    __shared__ float w_s[TA_ROWS * TA_MAX_SPLITS], l_s[TA_ROWS * TA_MAX_SPLITS];
+                                                         const float* __restrict__ partial, int DVP, int TA_ROWS) {
+    __shared__ float w_s[64 * TA_MAX_SPLITS], l_s[64 * TA_MAX_SPLITS];      // heads of one group x shares
     const int tile = blockIdx.x, g = blockIdx.y, r = blockIdx.z, DV = a.vdim, rep = a.heads / a.kv_heads;
     const int m = tile_rows[(size_t)tile * rq + r];
     if (m < 0) return;
@@ -263,71 +265,95 @@ __global__ void __launch_bounds__(128) talk_merge_kernel(DlWindowAttnArgs a, con
     for (int idx = threadIdx.x; idx < rep * DV; idx += blockDim.x) {
         const int hg = idx / DV, c = idx - hg * DV;
         const float* p = base + (size_t)(r * rep + hg) * (DVP + 2) + c;
-        float acc = 0.f;                      // a share without pages wrote nothing and weighs 0
-        for (int k = 0; k < n_splits; ++k) {
-            const float w = w_s[hg * n_splits + k];
-            if (w != 0.f) acc = fmaf(w, p[(size_t)k * TA_ROWS * (DVP + 2)], acc);
-        }
+        float acc = 0.f;                      // a share without pages left zeros and weighs 0: every load can go out at once
+#pragma unroll 8
+        for (int k = 0; k < n_splits; ++k) acc = fmaf(w_s[hg * n_splits + k], p[(size_t)k * TA_ROWS * (DVP + 2)], acc);
         a.out[(size_t)m * a.ldo + (size_t)(g * rep + hg) * DV + c] = acc;
     }
 }
 
 static int ta_dk(int dim) { return dim <= 32 ? 2 : dim <= 64 ? 4 : 8; }
-static int ta_nv(int vdim) { return vdim <= 32 ? 4 : vdim <= 64 ? 8 : vdim <= 96 ? 12 : 16; }
-static size_t ta_smem(int dim, int vdim, int key_heads) {
+static int ta_nv(int vdim) { return vdim <= 64 ? 8 : vdim <= 96 ? 12 : 16; }
+static size_t ta_smem(int dim, int vdim, int key_heads, int rows) {
     const int KH = key_heads > 1 ? key_heads : 1, QDP = KH * 16 * ta_dk(dim);
-    return ((size_t)2 * TA_PAGE * ta_stride(QDP + 8 * ta_nv(vdim)) + (size_t)TA_ROWS * ta_stride(QDP)) * sizeof(__nv_bfloat16);
+    return ((size_t)2 * TA_PAGE * ta_stride(QDP + 8 * ta_nv(vdim)) + (size_t)rows * ta_stride(QDP)) * sizeof(__nv_bfloat16);
+}
+#define TA_SMEM_MAX (220 * 1024)
+
+// Stacked rows of a tile for portions of `longest` rows of a sequence: 128 where long portions fit the shared memory, 16
+// for decoding (at most 16 query heads per key/value head), else 64; 0: the sizes do not fit at all.
+extern "C" int dl_talk_tc_tile_rows(int heads, int kv_heads, int dim, int vdim, int key_heads, int longest) {
+    if (heads < 1 || kv_heads < 1 || heads % kv_heads) return 0;
+    const int rep = heads / kv_heads;
+    if (rep <= 16 && longest <= 16 / rep && ta_smem(dim, vdim, key_heads, 16) <= TA_SMEM_MAX) return 16;
+    if (rep <= 128 && longest > 64 / rep && ta_smem(dim, vdim, key_heads, 128) <= TA_SMEM_MAX) return 128;
+    if (rep <= 64 && ta_smem(dim, vdim, key_heads, 64) <= TA_SMEM_MAX) return 64;
+    return 0;
 }
 
 // 0 if the kernel takes these sizes: a bf16 cache, dim and vdim multiples of 8 up to 128, at most 64 query heads per
 // key/value head, and a tile's queries plus two pages of all key heads within the shared memory of an SM
 extern "C" int dl_talk_attention_tc_supported(int heads, int kv_heads, int dim, int vdim, int key_heads, int ctype) {
-    if (ctype != DL_T_BF16 || heads < 1 || kv_heads < 1 || heads % kv_heads || heads / kv_heads > TA_ROWS) return -1;
+    if (ctype != DL_T_BF16 || heads < 1 || kv_heads < 1 || heads % kv_heads || heads / kv_heads > 64) return -1;
     if (dim < 8 || dim % 8 || dim > 128 || vdim < 8 || vdim % 8 || vdim > 128) return -1;
     if (key_heads > 1 && key_heads != kv_heads) return -1;
-    if (ta_smem(dim, vdim, key_heads) > 200 * 1024) return -1;
+    if (ta_smem(dim, vdim, key_heads, 64) > TA_SMEM_MAX) return -1;
     return 0;
 }
 
-extern "C" long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int vdim) {
-    return (long long)n_tiles * kv_heads * n_splits * TA_ROWS * (8 * ta_nv(vdim) + 2);
+// partial sums of the page shares: tiles x key/value heads x shares x stacked rows (rq rows x heads of a group, rounded up
+// to the kernel's 16, 64 or 128)
+static int ta_rows_of(int rq, int rep) { return rq * rep <= 16 ? 16 : rq * rep <= 64 ? 64 : 128; }
+extern "C" long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int vdim, int rows) {
+    return (long long)n_tiles * kv_heads * n_splits * rows * (8 * ta_nv(vdim) + 2);
+}
+
+template <int DK, int NV, int NR>
+static int launch_talk_nr(const DlWindowAttnArgs& a, const int* tile_rows, int n_tiles, int rq, int n_splits, float* partial, cudaStream_t st) {
+    const size_t smem = ta_smem(a.dim, a.vdim, a.key_heads, 16 * NR);
+    if (smem > TA_SMEM_MAX) { dl_set_error("dl_talk_attention_tc: %zu bytes of shared memory", smem); return -1; }
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<DK, NV, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { dl_set_error("dl_talk_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
+    }
+    talk_attention_mma_kernel<DK, NV, NR><<<dim3(n_tiles, a.kv_heads, n_splits), NR == 8 ? 256 : 128, smem, st>>>(a, tile_rows, rq, n_splits, partial);
+    return 0;
 }
 
 template <int DK, int NV>
-static int launch_talk(const DlWindowAttnArgs& a, const int* tile_rows, int n_tiles, int rq, int n_splits, float* partial, size_t smem, cudaStream_t st) {
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<DK, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { dl_set_error("dl_talk_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
-    }
-    talk_attention_mma_kernel<DK, NV><<<dim3(n_tiles, a.kv_heads, n_splits), 128, smem, st>>>(a, tile_rows, rq, n_splits, partial);
-    return 0;
+static int launch_talk(const DlWindowAttnArgs& a, const int* tile_rows, int n_tiles, int rq, int n_splits, float* partial, cudaStream_t st) {
+    const int rows = ta_rows_of(rq, a.heads / a.kv_heads);
+    if (rows == 16) return launch_talk_nr<DK, NV, 1>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    if (rows == 64) return launch_talk_nr<DK, NV, 4>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    return launch_talk_nr<DK, NV, 8>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
 }
 
-// tile_rows[n_tiles][rq] (device; -1 where a tile has fewer rows): up to rq = 64 / (heads / kv_heads) consecutive rows of
-// one sequence per tile.  q: [M][heads][max(key_heads, 1) * dim].  n_splits > 1: that many CTAs share each tile's pages
-// and leave partial sums in `partial` (dl_talk_tc_partial_floats() f32) that a merge launch combines.
+// tile_rows[n_tiles][rq] (device; -1 where a tile has fewer rows): up to rq consecutive rows of one sequence per tile,
+// rq * (heads / kv_heads) <= 128 stacked rows (dl_talk_tc_tile_rows() / (heads / kv_heads) is the rq to use).
+// q: [M][heads][max(key_heads, 1) * dim].  n_splits > 1: that many CTAs share each tile's pages and leave partial sums in
+// `partial` (dl_talk_tc_partial_floats() f32) that a merge launch combines.
 extern "C" int dl_talk_attention_tc(const DlWindowAttnArgs* args, const int* tile_rows, int n_tiles, int rq, int n_splits,
                                     float* partial, void* stream) {
     const DlWindowAttnArgs& a = *args;
     if (a.page_size != TA_PAGE || a.softcap != 0.f || a.rope_dims != 0 || a.window < 0 || a.chunk < 0 ||
         dl_talk_attention_tc_supported(a.heads, a.kv_heads, a.dim, a.vdim, a.key_heads, a.ctype) != 0 || rq < 1 ||
-        rq * (a.heads / a.kv_heads) > TA_ROWS || (a.ldq & 3) || (a.ldo & 1) || ((uintptr_t)a.q & 15) || ((uintptr_t)a.out & 7)) {
+        rq * (a.heads / a.kv_heads) > TA_MAX_ROWS || (a.ldq & 3) || (a.ldo & 1) || ((uintptr_t)a.q & 15) || ((uintptr_t)a.out & 7)) {
         dl_set_error("dl_talk_attention_tc: sizes not supported (heads %d / %d, dim %d, vdim %d, key heads %d, rq %d)", a.heads, a.kv_heads, a.dim, a.vdim, a.key_heads, rq);
         return -1;
     }
     if (n_tiles < 1) return 0;
     if (n_splits < 1 || n_splits > TA_MAX_SPLITS || (n_splits > 1 && partial == nullptr)) { dl_set_error("dl_talk_attention_tc: n_splits %d without scratch", n_splits); return -1; }
-    const size_t smem = ta_smem(a.dim, a.vdim, a.key_heads);
     cudaStream_t st = (cudaStream_t)stream;
     const int dk = ta_dk(a.dim), nv = ta_nv(a.vdim);
     int rc = -1;
-#define TA_CASE(DK_, NV_) if (dk == DK_ && nv == NV_) rc = launch_talk<DK_, NV_>(a, tile_rows, n_tiles, rq, n_splits, partial, smem, st);
-    TA_CASE(2, 4) TA_CASE(2, 8) TA_CASE(2, 12) TA_CASE(2, 16)
-    TA_CASE(4, 4) TA_CASE(4, 8) TA_CASE(4, 12) TA_CASE(4, 16)
-    TA_CASE(8, 4) TA_CASE(8, 8) TA_CASE(8, 12) TA_CASE(8, 16)
+#define TA_CASE(DK_, NV_) if (dk == DK_ && nv == NV_) rc = launch_talk<DK_, NV_>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    TA_CASE(2, 8) TA_CASE(2, 12) TA_CASE(2, 16)
+    TA_CASE(4, 8) TA_CASE(4, 12) TA_CASE(4, 16)
+    TA_CASE(8, 8) TA_CASE(8, 12) TA_CASE(8, 16)
 #undef TA_CASE
     if (rc != 0) return rc;
-    if (n_splits > 1) talk_merge_kernel<<<dim3(n_tiles, a.kv_heads, rq), 128, 0, st>>>(a, tile_rows, rq, n_splits, partial, 8 * nv);
+    if (n_splits > 1)
+        talk_merge_kernel<<<dim3(n_tiles, a.kv_heads, rq), 128, 0, st>>>(a, tile_rows, rq, n_splits, partial, 8 * nv, ta_rows_of(rq, a.heads / a.kv_heads));
     LAYER_CHECK_LAUNCH("dl_talk_attention_tc");
     return 0;
 }

@@ -75,12 +75,13 @@ __global__ void __launch_bounds__(256) window_kv_write_kernel(DlWindowKvArgs a) 
     }
 }
 
-// Separate values: one CTA per row, a warp per (query or key) head.  Optional rotary on the first rope_dims dimensions
-// of every head (pairs (i, i + rope_dims / 2) with rope_half, else (2i, 2i + 1); cos and sin of the row's angles are
-// formed once, in f64), THEN, with qk_norm, every head is divided by sqrt(mean(head^2) + eps): the queries in place, the
-// keys on their way into the cache.  The values are copied behind the keys.  With `talk` the head mix of the scores is
-// folded into the queries: q_mixed[h][c * dim + i] = sum over the query heads g of key/value head c of talk[h][g] q_g[i].
-// Dynamic shared memory: (kv_heads + q_heads) * dim + rope_dims floats.
+// Separate values: one CTA per row.  The row's queries and keys (and the head mix) are brought into shared memory by all
+// threads at once; then a warp per (query or key) head: optional rotary on the first rope_dims dimensions (pairs
+// (i, i + rope_dims / 2) with rope_half, else (2i, 2i + 1); cos and sin of the row's angles are formed once, in f64),
+// THEN, with qk_norm, the head is divided by sqrt(mean(head^2) + eps): the queries in place, the keys on their way into
+// the cache.  The values are copied behind the keys.  With `talk` the head mix of the scores is folded into the queries:
+// q_mixed[h][c * dim + i] = sum over the query heads g of key/value head c of talk[h][g] q_g[i].
+// Dynamic shared memory: 2 (kv_heads + q_heads) dim + rope_dims + q_heads^2 floats.
 template <typename CT>
 __global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
     extern __shared__ float wk_sm[];
@@ -90,21 +91,31 @@ __global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
     const int LD = a.dim + a.vdim, D = a.dim, RD = a.rope_dims, half = RD / 2;
     CT* line0 = (CT*)a.cache + (((size_t)page * a.kv_heads) * WA_PAGE + pos % WA_PAGE) * LD;
     const size_t head_step = (size_t)WA_PAGE * LD;
-    const int nq = a.q ? a.q_heads : 0;
-    float* heads_s = wk_sm;                                   // [kv_heads + nq][D]: every head as it leaves (rotated, normalised)
+    const int nq = a.q ? a.q_heads : 0, nk = a.k ? a.kv_heads : 0;      // without k (a layer that reads another layer's cache): the queries only
+    float* raw_s = wk_sm;                                     // [kv_heads + nq][D]: the heads as projected
+    float* heads_s = raw_s + (size_t)(a.kv_heads + nq) * D;   // the same heads as they leave (rotated, normalised)
     float* cs = heads_s + (size_t)(a.kv_heads + nq) * D;      // [half] cos, then [half] sin
     float* sn = cs + half;
+    float* talk_s = sn + half;                                // [nq][nq]
+    for (int t = threadIdx.x; t < nk * D; t += blockDim.x) raw_s[t] = a.k[(size_t)m * a.ld + t];
+    for (int t = threadIdx.x; t < nq * D; t += blockDim.x) raw_s[(size_t)a.kv_heads * D + t] = a.q[(size_t)m * a.ldq + t];
+    if (a.talk != nullptr)
+        for (int t = threadIdx.x; t < nq * nq; t += blockDim.x) talk_s[t] = a.talk[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         double sd, cd;
         sincos((double)pos * a.freqs[i], &sd, &cd);
         cs[i] = (float)(cd * (double)a.rope_scale);
         sn[i] = (float)(sd * (double)a.rope_scale);
     }
-    if (half > 0) __syncthreads();
-    for (int h = (a.k ? 0 : a.kv_heads) + warp; h < a.kv_heads + nq; h += nw) {      // without k (a layer that reads another layer's cache): the queries only
+    // the values go straight from the projection into the cache
+    for (int t = threadIdx.x; a.v != nullptr && t < a.kv_heads * a.vdim; t += blockDim.x) {
+        const int g = t / a.vdim, i = t - g * a.vdim;
+        st_f(line0 + g * head_step + a.dim + i, a.v[(size_t)m * a.ldv + t]);
+    }
+    __syncthreads();
+    for (int h = (a.kv_heads - nk) + warp; h < a.kv_heads + nq; h += nw) {
         const bool is_k = h < a.kv_heads;
-        float* qh = is_k ? nullptr : a.q + (size_t)m * a.ldq + (size_t)(h - a.kv_heads) * D;
-        const float* src = is_k ? a.k + (size_t)m * a.ld + (size_t)h * D : qh;
+        const float* src = raw_s + (size_t)h * D;
         float* hs = heads_s + (size_t)h * D;
         float ss = 0.f;
         for (int i = lane; i < D; i += 32) {
@@ -121,17 +132,13 @@ __global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
             ss = fmaf(r, r, ss);
         }
         const float inv = a.qk_norm ? 1.f / sqrtf(warp_sum(ss) / (float)D + a.eps) : 1.f;
-        __syncwarp();                                         // every lane has read the head before it is rewritten in place
         if (is_k) {
             CT* dst = line0 + h * head_step;
             for (int i = lane; i < D; i += 32) st_f(dst + i, hs[i] * inv);
         } else {
+            float* qh = a.q + (size_t)m * a.ldq + (size_t)(h - a.kv_heads) * D;
             for (int i = lane; i < D; i += 32) { const float r = hs[i] * inv; hs[i] = r; qh[i] = r; }
         }
-    }
-    for (int t = threadIdx.x; a.v != nullptr && t < a.kv_heads * a.vdim; t += blockDim.x) {
-        const int g = t / a.vdim, i = t - g * a.vdim;
-        st_f(line0 + g * head_step + a.dim + i, a.v[(size_t)m * a.ldv + t]);
     }
     if (a.talk != nullptr && nq > 0) {
         __syncthreads();
@@ -140,7 +147,7 @@ __global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
         for (int t = threadIdx.x; t < nq * QD; t += blockDim.x) {
             const int h = t / QD, c = (t - h * QD) / D, i = t - h * QD - c * D;
             float acc = 0.f;
-            for (int g = c * rep; g < (c + 1) * rep; ++g) acc = fmaf(a.talk[h * nq + g], qs[(size_t)g * D + i], acc);
+            for (int g = c * rep; g < (c + 1) * rep; ++g) acc = fmaf(talk_s[h * nq + g], qs[(size_t)g * D + i], acc);
             a.q_mixed[(size_t)m * a.ld_qm + t] = acc;
         }
     }
@@ -152,7 +159,8 @@ extern "C" int dl_window_kv_write(const DlWindowKvArgs* args, int M, void* strea
         if ((a.k == nullptr) != (a.v == nullptr) || (a.k == nullptr && a.q == nullptr)) { dl_set_error("dl_window_kv_write: keys and values come together, or the queries alone"); return -1; }
         if (a.rope_dims < 0 || a.rope_dims > a.dim || (a.rope_dims & 1) || a.vdim < 1 || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: bad sizes (rope_dims %d, dim %d, vdim %d)", a.rope_dims, a.dim, a.vdim); return -1; }
         if (a.talk != nullptr && (a.q == nullptr || a.q_mixed == nullptr || a.q_heads % a.kv_heads)) { dl_set_error("dl_window_kv_write: the head mix needs q, q_mixed and whole groups of heads"); return -1; }
-        const size_t smem = ((size_t)(a.kv_heads + (a.q ? a.q_heads : 0)) * a.dim + a.rope_dims) * sizeof(float);
+        const int nq_ = a.q ? a.q_heads : 0;
+        const size_t smem = ((size_t)2 * (a.kv_heads + nq_) * a.dim + a.rope_dims + (a.talk ? (size_t)nq_ * nq_ : 0)) * sizeof(float);
         if (smem > 227 * 1024) { dl_set_error("dl_window_kv_write: %zu bytes of shared memory", smem); return -1; }
         cudaError_t e;
         if (a.ctype == DL_T_BF16) {

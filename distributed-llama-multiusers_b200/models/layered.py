@@ -448,15 +448,17 @@ class WindowAttentionMixer:
         self.cache = torch.zeros(eng.n_pages, G, PAGE, self.line, dtype=eng.wdtype, device=eng.device) if self.kv_from is None else None
         # bf16 caches of sizes the tensor-core kernel takes: tiles of tc_rq consecutive rows of a sequence (0: per-row kernel)
         L = eng.L
-        self.tc_rq, self.tc_talk = 0, False
-        self.partial_width = d                  # columns of a page share's partial sums
+        self.tc_rq, self.tc_rq_small, self.tc_talk = 0, 0, False
+        self.partial_floats = 0                 # scratch of the page shares, if it is not the windowed kernel's
         attn_tc = eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0"
         if attn_tc and dv == d and self.talk is None and L.window_tc_supported(H, G, d, 0 if self.own_v else self.rope_dims, eng.wdtype):
             self.tc_rq = L.window_tc_rows(H, G)
         elif attn_tc and self.own_v and self.softcap == 0.0 and L.talk_tc_supported(H, G, d, dv, G if self.talk is not None else 0, eng.wdtype):
             # values wider or narrower than the keys, head-mixed scores: the tile kernel of talk_attention.cu
-            self.tc_rq, self.tc_talk = L.window_tc_rows(H, G), True
-            self.partial_width = (dv + 31) // 32 * 32
+            # tiles of 128 stacked (row, head) pairs for long portions, of 16 for decoding, 64 where those do not fit
+            kh = G if self.talk is not None else 0
+            self.tc_rq, self.tc_rq_small, self.tc_talk = L.talk_tc_rows(H, G, d, dv, kh, 1 << 30), L.talk_tc_rows(H, G, d, dv, kh, 1), True
+            self.partial_floats = L.talk_tc_partial_floats(WINDOW_CTAS_PER_SM * eng.n_sms, 1, 1, dv, self.tc_rq, H)
 
     def scratch(self) -> Dict[str, int]:
         n = {"qk": (self.H + self.G) * self.dim + (self.G * self.vdim if self.own_v else 0), "o": self.H * self.vdim}
@@ -503,7 +505,8 @@ class WindowAttentionMixer:
         if self.talk is not None:
             opts["key_heads"] = G
         if self.tc_rq:
-            tile_rows, n_tiles = e.window_tiles(self.tc_rq)
+            rq = self.tc_rq_small if self.tc_rq_small and e.longest <= self.tc_rq_small else self.tc_rq
+            tile_rows, n_tiles = e.window_tiles(rq)
             # few tiles (decoding): several CTAs share a tile's pages.  The share count depends on the tiling only (not on
             # the positions), so a captured graph stays valid as the sequences grow
             span = self.window or self.chunk
@@ -511,13 +514,13 @@ class WindowAttentionMixer:
             n_splits = 1
             if n_tiles * G <= 2 * e.n_sms:
                 n_splits = max(1, min(pages, WINDOW_MAX_SPLITS, (WINDOW_CTAS_PER_SM * e.n_sms) // (n_tiles * G)))
-            partial = e.window_partial(self.partial_width) if n_splits > 1 else None
+            partial = e.window_partial(d, self.partial_floats) if n_splits > 1 else None
             if self.tc_talk:
                 L.talk_attention_tc(q_in, o, H, G, d, dv, self.scale, self.window, e.pos, e.slot, e.block_table, self.cache, tile_rows,
-                                    n_tiles, self.tc_rq, n_splits, partial, chunk=self.chunk, sink=self.sink, key_heads=opts.get("key_heads", 0))
+                                    n_tiles, rq, n_splits, partial, chunk=self.chunk, sink=self.sink, key_heads=opts.get("key_heads", 0))
             else:
                 L.window_attention_tc(qk, o, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
-                                      self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, partial, **opts)
+                                      self.cache, tile_rows, n_tiles, rq, n_splits, partial, **opts)
         else:
             L.window_attention(q_in, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
                                self.cache, **opts)
@@ -762,6 +765,8 @@ class LayerListEngine:
             tensor_cores = os.environ.get("DLLAMA_LAYERS_TC", "1") != "0"
         self.tc = bool(tensor_cores) and self.round_x and int(max_rows) >= TC_MIN_ROWS
         self._kmax = 0
+        self.n_sms = L.sm_count()
+        self.longest = 0                         # rows of the longest portion of the current batch
         self.max_rows, self.n_slots = int(max_rows), int(n_slots)
         self.seq_len = self.cfg.seq_len = int(max_seq_len)
         self.max_pages = (self.seq_len + PAGE - 1) // PAGE
@@ -799,7 +804,6 @@ class LayerListEngine:
             self._attn_rq_big = max(1, min(16, 64 // hmax))
             if any(L.latent_tc_supported(mx.H, mx.rank, mx.dr, self.wdtype, self._attn_rq_big) for mx in att):
                 self.attn_rq = self._attn_rq_small = rq
-        self.n_sms = L.sm_count()
         self._n_tiles = self._n_splits = 0
         self._attn_partial = None
         if self.attn_rq:
@@ -855,12 +859,12 @@ class LayerListEngine:
         self._desc_len = self._chunks_off + 2 * self._max_chunks
         # then, per tile height rq of the windowed-attention layers, tile_rows [tiles][rq] of their tensor-core kernel
         self._window_partial = None
-        wd = [mx.partial_width for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq]
-        if wd:
-            self.window_partial(max(wd))               # allocated before any graph is captured
+        for mx in mixers:                              # allocated before any graph is captured
+            if isinstance(mx, WindowAttentionMixer) and mx.tc_rq:
+                self.window_partial(mx.dim, mx.partial_floats)
         self._wtile_off: Dict[int, int] = {}
         self._wtile_n: Dict[int, int] = {}
-        for rq in sorted({mx.tc_rq for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq}):
+        for rq in sorted({r for mx in mixers if isinstance(mx, WindowAttentionMixer) for r in (mx.tc_rq, mx.tc_rq_small) if r}):
             self._wtile_off[rq] = self._desc_len
             self._desc_len += ((R + rq - 1) // rq + S) * rq
         self.tile_rows = None
@@ -957,9 +961,9 @@ class LayerListEngine:
             return None
         return (self.tile_rows, self._n_tiles, self.attn_rq, self._n_splits, self._attn_partial)
 
-    def window_partial(self, dim: int) -> torch.Tensor:
-        """Scratch of the windowed-attention kernel's page shares: tiles x key/value heads x shares <= WINDOW_CTAS_PER_SM x SMs."""
-        need = self.L.window_tc_partial_floats(WINDOW_CTAS_PER_SM * self.n_sms, 1, 1, dim)
+    def window_partial(self, dim: int, floats: int = 0) -> torch.Tensor:
+        """Scratch of the attention tile kernels' page shares: tiles x key/value heads x shares <= WINDOW_CTAS_PER_SM x SMs."""
+        need = floats or self.L.window_tc_partial_floats(WINDOW_CTAS_PER_SM * self.n_sms, 1, 1, dim)
         if self._window_partial is None or self._window_partial.numel() < need:
             self._window_partial = torch.zeros(need, dtype=torch.float32, device=self.device)
         return self._window_partial
@@ -1054,7 +1058,7 @@ class LayerListEngine:
                     hd[wo + nt * rq + len(part):wo + (nt + 1) * rq] = -1
                     nt += 1
             self._wtile_n[rq] = nt
-        longest = max(len(r) for r in by_slot.values())
+        self.longest = longest = max(len(r) for r in by_slot.values())
         self.lightning_chunks = 0
         if self._lightning_scratch is not None and longest >= LIGHTNING_CHUNKED_MIN_ROWS:
             self.lightning_chunks = (longest + self.L.LIGHTNING_CHUNK - 1) // self.L.LIGHTNING_CHUNK

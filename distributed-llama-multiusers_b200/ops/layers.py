@@ -381,8 +381,15 @@ def talk_tc_supported(heads: int, kv_heads: int, dim: int, vdim: int, key_heads:
     return layers_lib().dl_talk_attention_tc_supported(heads, kv_heads, dim, vdim, key_heads, ctype) == 0
 
 
-def talk_tc_partial_floats(n_tiles: int, kv_heads: int, n_splits: int, vdim: int) -> int:
-    return int(layers_lib().dl_talk_tc_partial_floats(n_tiles, kv_heads, n_splits, vdim))
+def talk_tc_rows(heads: int, kv_heads: int, dim: int, vdim: int, key_heads: int, longest: int) -> int:
+    """Rows of one sequence per tile of the kernel for portions of up to `longest` rows: the tile stacks 16 (decoding), 64
+    or 128 (row, head-of-a-group) pairs, whichever fits the shared memory."""
+    return int(layers_lib().dl_talk_tc_tile_rows(heads, kv_heads, dim, vdim, key_heads, longest)) // (heads // kv_heads)
+
+
+def talk_tc_partial_floats(n_tiles: int, kv_heads: int, n_splits: int, vdim: int, rq: int, heads: int) -> int:
+    stacked = rq * (heads // kv_heads)
+    return int(layers_lib().dl_talk_tc_partial_floats(n_tiles, kv_heads, n_splits, vdim, 16 if stacked <= 16 else 64 if stacked <= 64 else 128))
 
 
 def talk_attention_tc(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, window: int,
@@ -393,22 +400,21 @@ def talk_attention_tc(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: 
     against the keys of all key/value heads side by side.  Tiles and page shares as in window_attention_tc."""
     a = _window_args(q, out, heads, kv_heads, dim, 0, scale, 0.0, window, pos, slot, block_table, cache, vdim, chunk, sink, key_heads)
     if n_splits > 1:
-        assert partial is not None and partial.numel() >= talk_tc_partial_floats(n_tiles, kv_heads, n_splits, vdim)
+        assert partial is not None and partial.numel() >= talk_tc_partial_floats(n_tiles, kv_heads, n_splits, vdim, rq, heads)
     check_layers(layers_lib().dl_talk_attention_tc(a, tile_rows.data_ptr(), n_tiles, rq, n_splits, _p(partial), _stream()),
                  "dl_talk_attention_tc")
     lib.count_launch(2 if n_splits > 1 else 1)
 
 
-def talk_attention_tiles(q, out, heads, kv_heads, dim, vdim, scale, window, pos, slot, block_table, cache, tiles, n_splits: int = 1,
+def talk_attention_tiles(q, out, heads, kv_heads, dim, vdim, scale, window, pos, slot, block_table, cache, tiles, rq: int, n_splits: int = 1,
                          chunk: int = 0, sink: Optional[torch.Tensor] = None, key_heads: int = 0):
-    """Convenience for callers with host-side tiles (lists of row indices of one sequence, consecutive positions)."""
-    rq = window_tc_rows(heads, kv_heads)
+    """Convenience for callers with host-side tiles (lists of up to rq row indices of one sequence, consecutive positions)."""
     t = torch.full((len(tiles), rq), -1, dtype=torch.int32)
     for i, rows in enumerate(tiles):
         t[i, :len(rows)] = torch.tensor(rows, dtype=torch.int32)
     partial = None
     if n_splits > 1:
-        partial = torch.zeros(talk_tc_partial_floats(len(tiles), kv_heads, n_splits, vdim), dtype=torch.float32, device=q.device)
+        partial = torch.zeros(talk_tc_partial_floats(len(tiles), kv_heads, n_splits, vdim, rq, heads), dtype=torch.float32, device=q.device)
     talk_attention_tc(q, out, heads, kv_heads, dim, vdim, scale, window, pos, slot, block_table, cache, t.to(q.device), len(tiles), rq,
                       n_splits, partial, chunk, sink, key_heads)
 

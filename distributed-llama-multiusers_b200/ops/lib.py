@@ -392,7 +392,8 @@ def layers_lib():
     L.dl_window_tc_partial_floats.restype = i64
     L.dl_talk_attention_tc_supported.argtypes = [i32, i32, i32, i32, i32, i32]
     L.dl_talk_attention_tc.argtypes = [C.POINTER(DlWindowAttnArgs), vp, i32, i32, i32, vp, vp]
-    L.dl_talk_tc_partial_floats.argtypes = [i32, i32, i32, i32]
+    L.dl_talk_tc_partial_floats.argtypes = [i32, i32, i32, i32, i32]
+    L.dl_talk_tc_tile_rows.argtypes = [i32, i32, i32, i32, i32, i32]
     L.dl_talk_tc_partial_floats.restype = i64
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
@@ -420,7 +421,7 @@ def layers_lib():
                  "dl_mamba_conv", "dl_mamba_scan", "dl_mamba_scan_chunked", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
                  "dl_gemm_wh_tc", "dl_hyper_step", "dl_window_kv_write", "dl_window_attention", "dl_moe_select", "dl_moe_rows", "dl_moe_plan",
                  "dl_moe_combine", "dl_xh_gather_rows", "dl_gemm_wh_tc_grouped", "dl_window_tc_rows", "dl_window_attention_tc_supported",
-                 "dl_window_attention_tc", "dl_talk_attention_tc_supported", "dl_talk_attention_tc", "dl_causal_conv", "dl_poly_norm", "dl_lightning_scan", "dl_lightning_scan_chunked"):
+                 "dl_window_attention_tc", "dl_talk_attention_tc_supported", "dl_talk_attention_tc", "dl_talk_tc_tile_rows", "dl_causal_conv", "dl_poly_norm", "dl_lightning_scan", "dl_lightning_scan_chunked"):
         getattr(L, name).restype = i32
     _layers = L
     return L

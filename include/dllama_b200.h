@@ -594,7 +594,9 @@ int dl_window_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* til
 /* The tile kernel for values of a width of their own (vdim > 0, any multiple of 8 up to 128; rope_dims 0, no soft cap) and
  * for head-mixed scores (key_heads = kv_heads: q [M][heads][kv_heads * dim], talk_attention.cu).  Tiles as above. */
 int dl_talk_attention_tc_supported(int heads, int kv_heads, int dim, int vdim, int key_heads, int ctype);
-long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int vdim);
+/* stacked (row x head-of-a-group) rows per tile for portions of `longest` rows: 16 (decoding), 64 or 128; rq = that / (heads / kv_heads) */
+int dl_talk_tc_tile_rows(int heads, int kv_heads, int dim, int vdim, int key_heads, int longest);
+long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int vdim, int tile_rows);
 int dl_talk_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* tile_rows, int n_tiles, int rq, int n_splits,
                          float* partial, void* stream);
 

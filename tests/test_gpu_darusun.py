@@ -144,9 +144,9 @@ def _attention_rows(q, k, v, talk, scale, rot, base, ctype, tc=False, portions=N
                           v=vv if write_kv else None, vdim=dv, qk_norm=True, eps=1e-5, rope_half=True, talk=tk, q_mixed=qm)
         o = torch.zeros(n, H * dv, device="cuda")
         if tc:
-            rq = L.window_tc_rows(H, G)
+            rq = L.talk_tc_rows(H, G, d, dv, G, n)          # tiles of 16, 64 or 128 stacked (row, head) pairs by the portion's length
             tiles = [list(range(i, min(i + rq, n))) for i in range(0, n, rq)]
-            L.talk_attention_tiles(qm, o, H, G, d, dv, scale, 0, pos, slot, table, cache, tiles, n_splits=n_splits, key_heads=G)
+            L.talk_attention_tiles(qm, o, H, G, d, dv, scale, 0, pos, slot, table, cache, tiles, rq, n_splits=n_splits, key_heads=G)
         else:
             L.window_attention(qm, o, n, H, G, d, 0, scale, 0.0, 0, pos, slot, table, cache, vdim=dv, key_heads=G)
         out.append(o.cpu())
