@@ -13,7 +13,8 @@
 // positions of one sequence and the query heads of ONE key/value head g: (position, head-of-the-group) pairs stack on the
 // M dimension, NR warps x 16 stacked rows: NR = 8 (256 threads, 128 stacked rows) for long portions, where a staged page
 // serves twice the queries; 4 for medium ones; 1 for decoding (one warp multiplies, all four stage; the small query tile
-// lets two CTAs share an SM).  Per page of 32 tokens it stages the keys of every key/value head and the values
+// lets two CTAs share an SM).  Decoding with 2 to 8 key/value heads runs the ALLG form instead: ONE CTA per tile, warp g
+// multiplies the heads of key/value head g, and the page staged for all of them holds every head's keys and values once.  Per page of 32 tokens it stages the keys of every key/value head and the values
 // of head g (cp.async, two buffers: page k + 1 is in flight while page k is multiplied), then per warp
 //     S[16 x 32]  = Q[16 x KH * DP] . K[32 x KH * DP]^T      Q (bf16, staged once per tile) and K by ldmatrix
 //     scale, mask, online softmax in f32 and base 2
@@ -41,22 +42,29 @@ __host__ __device__ __forceinline__ int ta_stride(int n) {      // bf16 elements
     return s;
 }
 
-template <int DK, int NV, int NR>
-__global__ void __launch_bounds__(NR == 8 ? 256 : 128) talk_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
+template <int DK, int NV, int NR, bool ALLG>
+__global__ void __launch_bounds__((NR == 8 || ALLG) ? 256 : 128) talk_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
                                                                 float* __restrict__ partial) {
-    constexpr int DP = 16 * DK, DVP = 8 * NV, TA_ROWS = 16 * NR, THREADS = NR == 8 ? 256 : 128;
+    constexpr int DP = 16 * DK, DVP = 8 * NV, TA_ROWS = 16 * NR;
+    const int THREADS = blockDim.x;
     extern __shared__ __align__(16) uint8_t smraw[];
     __shared__ int s_row[TA_ROWS];
     const int D = a.dim, DV = a.vdim, LD = D + DV;
     const int KH = a.key_heads > 1 ? a.key_heads : 1, QD = KH * D, QDP = KH * DP;
-    const int LDS = ta_stride(QDP + DVP), QS = ta_stride(QDP);
-    __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][TA_PAGE][LDS]: keys of all heads | values of head g
-    __nv_bfloat16* q_s = kv_s + (size_t)2 * TA_PAGE * LDS;                          // [TA_ROWS][QS]: the stacked queries
-    const int tile = blockIdx.x, g = blockIdx.y, rep = a.heads / a.kv_heads;
+    // staged line: [ keys of KS heads | values of VS heads ]; ALLG: every head's, else all (or this group's) keys and this group's values
+    const int KS = ALLG ? a.kv_heads : KH, VS = ALLG ? a.kv_heads : 1, VOFF = KS * DP;
+    const int LDS = ta_stride(VOFF + VS * DVP), QS = ta_stride(QDP);
+    __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][TA_PAGE][LDS]
+    __nv_bfloat16* q_s = kv_s + (size_t)2 * TA_PAGE * LDS;                          // [TA_ROWS (ALLG: per key/value head)][QS]: the stacked queries
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int tile = blockIdx.x, rep = a.heads / a.kv_heads;
+    const int g = ALLG ? min(warp, a.kv_heads - 1) : (int)blockIdx.y;              // ALLG: warp g multiplies key/value head g
+    const int wrow = ALLG ? 0 : warp;                                               // this warp's block of 16 stacked rows among its group's
+    const int qrow0 = ALLG ? g * 16 : warp * 16;                                    // ... and where that block's queries sit in q_s
     if (threadIdx.x < rq) s_row[threadIdx.x] = tile_rows[(size_t)tile * rq + threadIdx.x];
     // the padding of keys and values stays zero: the copies below never touch it
-    for (int i = threadIdx.x; i < 2 * TA_PAGE * LDS / 8; i += THREADS) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (D != DP || DV != DVP)
+        for (int i = threadIdx.x; i < 2 * TA_PAGE * LDS / 8; i += THREADS) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     int n_rows = 0;
     while (n_rows < rq && s_row[n_rows] >= 0) ++n_rows;
@@ -70,22 +78,23 @@ __global__ void __launch_bounds__(NR == 8 ? 256 : 128) talk_attention_mma_kernel
         pg_lo += (int)blockIdx.z * per;
         pg_hi = min(pg_hi, pg_lo + per - 1);
     }
-    const bool active = warp < NR && warp * 16 < n_rows * rep;
+    const bool active = ALLG ? warp < a.kv_heads : (warp < NR && warp * 16 < n_rows * rep);
     const float c1 = a.scale * TA_LOG2E;
 
     // this thread's two stacked rows: s = position-in-tile * rep + head-in-group
-    const int s0 = warp * 16 + gid, s1 = s0 + 8;
+    const int s0 = wrow * 16 + gid, s1 = s0 + 8;
     const int r0 = s0 / rep, r1 = s1 / rep;
     const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
     const int pos0 = p_first + r0, pos1 = p_first + r1;
     const int cs0 = a.chunk > 0 ? pos0 / a.chunk * a.chunk : 0, cs1 = a.chunk > 0 ? pos1 / a.chunk * a.chunk : 0;
     const int cs_last = a.chunk > 0 ? p_last / a.chunk * a.chunk : 0;
     // the tile's queries, rounded to bf16, zero-padded per key head
-    for (int idx = threadIdx.x; idx < TA_ROWS * (QDP / 4); idx += THREADS) {
+    for (int idx = threadIdx.x; idx < (ALLG ? a.kv_heads : 1) * TA_ROWS * (QDP / 4); idx += THREADS) {
         const int sr = idx / (QDP / 4), col = (idx - sr * (QDP / 4)) * 4;
-        const int c = col / DP, d = col - c * DP, r = sr / rep;
+        const int gq = ALLG ? sr / TA_ROWS : g, sg = ALLG ? sr % TA_ROWS : sr;      // key/value head and stacked row within it
+        const int c = col / DP, d = col - c * DP, r = sg / rep;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < n_rows && d < D) v = *reinterpret_cast<const float4*>(a.q + (size_t)s_row[r] * a.ldq + (size_t)(g * rep + sr % rep) * QD + c * D + d);
+        if (r < n_rows && d < D) v = *reinterpret_cast<const float4*>(a.q + (size_t)s_row[r] * a.ldq + (size_t)(gq * rep + sg % rep) * QD + c * D + d);
         uint2 pk;
         pk.x = pack_bf16(v.x, v.y);
         pk.y = pack_bf16(v.z, v.w);
@@ -96,19 +105,19 @@ __global__ void __launch_bounds__(NR == 8 ? 256 : 128) talk_attention_mma_kernel
     for (int v = 0; v < NV; ++v) { o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const int kch = D / 8, vch = DV / 8, per_line = KH * kch + vch;
+    const int kch = D / 8, vch = DV / 8, per_line = KS * kch + VS * vch;
     auto issue = [&](int pg, int buf) {
         const int page = a.block_table[(size_t)slot * a.max_pages + pg];
         const __nv_bfloat16* src0 = (const __nv_bfloat16*)a.cache + (size_t)page * a.kv_heads * TA_PAGE * LD;
         __nv_bfloat16* dst = kv_s + (size_t)buf * TA_PAGE * LDS;
         for (int i = threadIdx.x; i < TA_PAGE * per_line; i += THREADS) {
             const int j = i / per_line, part = i - j * per_line;
-            if (part < KH * kch) {
+            if (part < KS * kch) {
                 const int c = part / kch, p = part - c * kch;
-                cp_async16(dst + (size_t)j * LDS + c * DP + p * 8, src0 + ((size_t)(KH > 1 ? c : g) * TA_PAGE + j) * LD + p * 8);
+                cp_async16(dst + (size_t)j * LDS + c * DP + p * 8, src0 + ((size_t)(KS > 1 ? c : g) * TA_PAGE + j) * LD + p * 8);
             } else {
-                const int p = part - KH * kch;
-                cp_async16(dst + (size_t)j * LDS + QDP + p * 8, src0 + ((size_t)g * TA_PAGE + j) * LD + D + p * 8);
+                const int c = (part - KS * kch) / vch, p = part - KS * kch - c * vch;
+                cp_async16(dst + (size_t)j * LDS + VOFF + c * DVP + p * 8, src0 + ((size_t)(ALLG ? c : g) * TA_PAGE + j) * LD + D + p * 8);
             }
         }
     };
@@ -124,15 +133,16 @@ __global__ void __launch_bounds__(NR == 8 ? 256 : 128) talk_attention_mma_kernel
         float sc[4][4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+        const int kcol0 = (ALLG && KH == 1) ? g * DP : 0;      // plain grouped-query attention in the ALLG form: the group's own key among all staged
         for (int c = 0; c < KH; ++c) {
 #pragma unroll
             for (int kk = 0; kk < DK; ++kk) {
                 uint32_t qf[4];
-                ldmatrix_x4(qf, q_s + (size_t)(warp * 16 + (mat & 1) * 8 + rr) * QS + c * DP + kk * 16 + (mat >> 1) * 8);
+                ldmatrix_x4(qf, q_s + (size_t)(qrow0 + (mat & 1) * 8 + rr) * QS + c * DP + kk * 16 + (mat >> 1) * 8);
 #pragma unroll
                 for (int np = 0; np < 2; ++np) {
                     uint32_t b[4];
-                    ldmatrix_x4(b, kv + (size_t)(np * 16 + (mat >> 1) * 8 + rr) * LDS + c * DP + kk * 16 + (mat & 1) * 8);
+                    ldmatrix_x4(b, kv + (size_t)(np * 16 + (mat >> 1) * 8 + rr) * LDS + kcol0 + c * DP + kk * 16 + (mat & 1) * 8);
                     mma_bf16(sc[2 * np], qf, b[0], b[1]);
                     mma_bf16(sc[2 * np + 1], qf, b[2], b[3]);
                 }
@@ -186,7 +196,7 @@ __global__ void __launch_bounds__(NR == 8 ? 256 : 128) talk_attention_mma_kernel
             for (int vp = 0; vp < NV / 2; ++vp) {
                 const int vt = 2 * vp + (mat >> 1);
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, kv + (size_t)(ks * 16 + (mat & 1) * 8 + rr) * LDS + QDP + vt * 8);
+                ldmatrix_x4_trans(b, kv + (size_t)(ks * 16 + (mat & 1) * 8 + rr) * LDS + VOFF + (ALLG ? g * DVP : 0) + vt * 8);
                 mma_bf16(o[2 * vp], pa, b[0], b[1]);
                 mma_bf16(o[2 * vp + 1], pa, b[2], b[3]);
             }
@@ -265,9 +275,13 @@ __global__ void __launch_bounds__(128) talk_merge_kernel(DlWindowAttnArgs a, con
     for (int idx = threadIdx.x; idx < rep * DV; idx += blockDim.x) {
         const int hg = idx / DV, c = idx - hg * DV;
         const float* p = base + (size_t)(r * rep + hg) * (DVP + 2) + c;
-        float acc = 0.f;                      // a share without pages left zeros and weighs 0: every load can go out at once
-#pragma unroll 8
-        for (int k = 0; k < n_splits; ++k) acc = fmaf(w_s[hg * n_splits + k], p[(size_t)k * TA_ROWS * (DVP + 2)], acc);
+        float acc = 0.f;                      // shares that weigh nothing (no visible key in their pages) are not read; the other loads go out together
+#pragma unroll 4
+        for (int k = 0; k < n_splits; ++k) {
+            const float w = w_s[hg * n_splits + k];
+            const float v = w != 0.f ? p[(size_t)k * TA_ROWS * (DVP + 2)] : 0.f;
+            acc = fmaf(w, v, acc);
+        }
         a.out[(size_t)m * a.ldo + (size_t)(g * rep + hg) * DV + c] = acc;
     }
 }
@@ -278,7 +292,15 @@ static size_t ta_smem(int dim, int vdim, int key_heads, int rows) {
     const int KH = key_heads > 1 ? key_heads : 1, QDP = KH * 16 * ta_dk(dim);
     return ((size_t)2 * TA_PAGE * ta_stride(QDP + 8 * ta_nv(vdim)) + (size_t)rows * ta_stride(QDP)) * sizeof(__nv_bfloat16);
 }
+// the ALLG form: every head's keys and values in a staged line, 16 stacked rows of queries per key/value head
+static size_t ta_smem_allg(int dim, int vdim, int key_heads, int kv_heads) {
+    const int KH = key_heads > 1 ? key_heads : 1, DP = 16 * ta_dk(dim);
+    return ((size_t)2 * TA_PAGE * ta_stride(kv_heads * (DP + 8 * ta_nv(vdim))) + (size_t)kv_heads * 16 * ta_stride(KH * DP)) * sizeof(__nv_bfloat16);
+}
 #define TA_SMEM_MAX (220 * 1024)
+static bool ta_allg(int kv_heads, int dim, int vdim, int key_heads) {
+    return kv_heads >= 2 && kv_heads <= 8 && ta_smem_allg(dim, vdim, key_heads, kv_heads) <= TA_SMEM_MAX;
+}
 
 // Stacked rows of a tile for portions of `longest` rows of a sequence: 128 where long portions fit the shared memory, 16
 // for decoding (at most 16 query heads per key/value head), else 64; 0: the sizes do not fit at all.
@@ -308,24 +330,29 @@ extern "C" long long dl_talk_tc_partial_floats(int n_tiles, int kv_heads, int n_
     return (long long)n_tiles * kv_heads * n_splits * rows * (8 * ta_nv(vdim) + 2);
 }
 
-template <int DK, int NV, int NR>
+template <int DK, int NV, int NR, bool ALLG>
 static int launch_talk_nr(const DlWindowAttnArgs& a, const int* tile_rows, int n_tiles, int rq, int n_splits, float* partial, cudaStream_t st) {
-    const size_t smem = ta_smem(a.dim, a.vdim, a.key_heads, 16 * NR);
+    const size_t smem = ALLG ? ta_smem_allg(a.dim, a.vdim, a.key_heads, a.kv_heads) : ta_smem(a.dim, a.vdim, a.key_heads, 16 * NR);
     if (smem > TA_SMEM_MAX) { dl_set_error("dl_talk_attention_tc: %zu bytes of shared memory", smem); return -1; }
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<DK, NV, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<DK, NV, NR, ALLG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { dl_set_error("dl_talk_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
     }
-    talk_attention_mma_kernel<DK, NV, NR><<<dim3(n_tiles, a.kv_heads, n_splits), NR == 8 ? 256 : 128, smem, st>>>(a, tile_rows, rq, n_splits, partial);
+    const dim3 grid(n_tiles, ALLG ? 1 : a.kv_heads, n_splits);
+    const int threads = ALLG ? (a.kv_heads > 4 ? 256 : 128) : (NR == 8 ? 256 : 128);
+    talk_attention_mma_kernel<DK, NV, NR, ALLG><<<grid, threads, smem, st>>>(a, tile_rows, rq, n_splits, partial);
     return 0;
 }
 
 template <int DK, int NV>
 static int launch_talk(const DlWindowAttnArgs& a, const int* tile_rows, int n_tiles, int rq, int n_splits, float* partial, cudaStream_t st) {
     const int rows = ta_rows_of(rq, a.heads / a.kv_heads);
-    if (rows == 16) return launch_talk_nr<DK, NV, 1>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
-    if (rows == 64) return launch_talk_nr<DK, NV, 4>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
-    return launch_talk_nr<DK, NV, 8>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    // many small tiles (batched decoding): one CTA per tile stages every head's keys and values once; few (one stream): a CTA
+    // per key/value head, so that more SMs share the pages
+    if (rows == 16 && n_tiles * a.kv_heads * n_splits >= 512 && ta_allg(a.kv_heads, a.dim, a.vdim, a.key_heads)) return launch_talk_nr<DK, NV, 1, true>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    if (rows == 16) return launch_talk_nr<DK, NV, 1, false>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    if (rows == 64) return launch_talk_nr<DK, NV, 4, false>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
+    return launch_talk_nr<DK, NV, 8, false>(a, tile_rows, n_tiles, rq, n_splits, partial, st);
 }
 
 // tile_rows[n_tiles][rq] (device; -1 where a tile has fewer rows): up to rq consecutive rows of one sequence per tile,

@@ -56,6 +56,7 @@ import numpy as np
 import torch
 
 from ..formats.safetensors import SafetensorsFile
+from .memory import graph_capture
 from .paging import PAGE, PageAllocator
 
 
@@ -1173,7 +1174,7 @@ class LayerListEngine:
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = _lib.launch_count
-            with torch.cuda.graph(g, stream=self._graph_stream):
+            with graph_capture(g, self._graph_stream):
                 self._launch_step(M, n_logits, greedy)
             self._graph_launches[key] = _lib.launch_count - n0
             _lib.launch_count = n0

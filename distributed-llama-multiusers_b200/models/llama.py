@@ -30,6 +30,7 @@ from ..ops import kernels as K
 from ..ops import quant
 from ..ops.lib import EPI_QKV_ROPE, EPI_SILU_MUL, EPI_STORE
 from ..parallel.symm import SymmetricBuffer, validate_tp
+from .memory import graph_capture
 from .oracle import rope_frequencies
 from .paging import PageAllocator        # noqa: F401  (also imported from here by older callers)
 
@@ -591,7 +592,7 @@ class LlamaEngine:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = K.lib.launch_count
-            with torch.cuda.graph(g, stream=self._graph_stream):
+            with graph_capture(g, self._graph_stream):
                 self._launch_forward(M, row0, greedy, device_loop, chunk)
             self._graph_launches[key] = K.lib.launch_count - n0
             K.lib.launch_count = n0          # capture enqueued nothing

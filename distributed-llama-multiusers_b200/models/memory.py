@@ -3,6 +3,8 @@ which sums the pipes and buffers of the node's graph).  Used by the CLI banner a
 the 180 GB of a B200 before anything is loaded (e.g. Llama-3.1-405B Q40 at TP=8)."""
 from __future__ import annotations
 
+import contextlib
+import gc
 from typing import Dict
 
 from ..formats.mfile import LlmHeader
@@ -52,3 +54,20 @@ def describe(m: Dict[str, int]) -> str:
     extra = f", fp16 weight copy {mb(m['fp16_weight_copy'])}" if m.get("fp16_weight_copy") else ""
     return (f"📀 RequiredMemory: {mb(m['total'])} (weights {mb(m['weights'])}, embedding {mb(m['embedding'])}, "
             f"kv {mb(m['kv_cache'])}, activations {mb(m['activations'])}{extra})")
+
+
+@contextlib.contextmanager
+def graph_capture(graph, stream):
+    """Capture the launches of the body into `graph`.  Python's cyclic collector stays off meanwhile: if it ran inside
+    the capture it could free device or pinned memory of objects that died earlier (an engine that was closed, say), and
+    a free is not allowed while a stream captures -- the capture would be invalidated, at a moment no test controls.  Only
+    this thread's calls are held to the capture's rules, so other threads (an HTTP front end) may use CUDA meanwhile."""
+    import torch
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            yield
+    finally:
+        if was_on:
+            gc.enable()

@@ -13,6 +13,10 @@
       the chunk-parallel linear-attention scan alone (2048 rows of one sequence, 16 heads of 128 x 128), timed with CUDA
       events, then the token-by-token kernel on 32 sequences of one row:
         ncu --set full --clock-control none -k regex:lightning_chunk_out -s 1 -c 2 -o out python scripts/profile_layered.py lightning-scan
+  python scripts/profile_layered.py talk-attention
+      the head-mixed attention tile kernel alone (2048 rows of one sequence, 16 / 4 heads, keys and values of 128, 64
+      rotated dims, the head mix folded into queries of 4 x 128), timed with CUDA events:
+        ncu --set full --clock-control none -k regex:talk_attention_mma -s 1 -c 1 -o out python scripts/profile_layered.py talk-attention
 Run the plain command first; capture only if it exits 0.
 """
 import argparse
@@ -81,6 +85,42 @@ def window_attention(a):
     print("GFLOP over the visible keys: %.2f" % (keys * H * d * 4 / 1e9))
 
 
+def talk_attention(a):
+    import torch
+    from dllama_b200.models.layered import rotary_frequencies
+    from dllama_b200.ops import layers as L
+    H, G, d, dv, rd, n = 16, 4, 128, 128, 64, 2048
+    n_pages = n // 32
+    bt = torch.arange(n_pages, dtype=torch.int32).view(1, -1).cuda()
+    cache = torch.zeros(n_pages, G, 32, d + dv, dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(n, w, generator=g).cuda() for w in (H * d, G * d, G * dv))
+    talk = (torch.eye(H) + torch.randn(H, H, generator=g) * 0.3).cuda()
+    qm = torch.zeros(n, H * G * d, device="cuda")
+    pos, slot = torch.arange(n, dtype=torch.int32).cuda(), torch.zeros(n, dtype=torch.int32).cuda()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        ev0.record()
+        L.window_kv_write(k, n, G, d, rd, rotary_frequencies(500000.0, rd).cuda(), 1.0, pos, slot, bt, cache, q=q, q_heads=H, v=v, vdim=dv,
+                          qk_norm=True, eps=1e-5, rope_half=True, talk=talk, q_mixed=qm)
+        ev1.record()
+        torch.cuda.synchronize()
+        print("cache writer (rotary, unit norms, head mix): %.1f us" % (ev0.elapsed_time(ev1) * 1e3))
+    out = torch.zeros(n, H * dv, device="cuda")
+    rq = L.talk_tc_rows(H, G, d, dv, G, n)
+    tiles = torch.arange(n, dtype=torch.int32).view(-1, rq).cuda()
+    for n_splits in (1, 4):
+        part = torch.zeros(L.talk_tc_partial_floats(n // rq, G, n_splits, dv, rq, H), device="cuda") if n_splits > 1 else None
+        for _ in range(4):
+            ev0.record()
+            L.talk_attention_tc(qm, out, H, G, d, dv, 0.1, 0, pos, slot, bt, cache, tiles, n // rq, rq, n_splits, part, key_heads=G)
+            ev1.record()
+            torch.cuda.synchronize()
+            print("head-mixed attention, tiles of %d rows, %d page shares: %.1f us" % (rq, n_splits, ev0.elapsed_time(ev1) * 1e3))
+    pairs = n * (n + 1) // 2
+    print("FLOPs per launch (visible pairs, folded form 2 * (4 * 128 + 128) per head): %.1f G" % (pairs * H * 2 * (G * d + dv) / 1e9))
+
+
 def lightning_scan(a):
     import torch
     from dllama_b200.ops import layers as L
@@ -115,11 +155,11 @@ def lightning_scan(a):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=("steps", "window-attention", "lightning-scan"))
+    ap.add_argument("what", choices=("steps", "window-attention", "lightning-scan", "talk-attention"))
     ap.add_argument("--design", default="sunesun", choices=("ribivik", "sunesun", "venadra", "darusun"))
     ap.add_argument("--size", default="w2048")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--model-dir", default="/tmp")
     a = ap.parse_args()
-    {"steps": steps, "window-attention": window_attention, "lightning-scan": lightning_scan}[a.what](a)
+    {"steps": steps, "window-attention": window_attention, "lightning-scan": lightning_scan, "talk-attention": talk_attention}[a.what](a)

@@ -120,7 +120,7 @@ def _assert_same(got, ref, what, tol=0.02):
 # ---------------------------------------------------------------------------------------------------------------------
 # mechanisms alone: head-mixed attention
 # ---------------------------------------------------------------------------------------------------------------------
-def _attention_rows(q, k, v, talk, scale, rot, base, ctype, tc=False, portions=None, n_splits=1, write_kv=True, cache=None):
+def _attention_rows(q, k, v, talk, scale, rot, base, ctype, tc=False, portions=None, n_splits=1, write_kv=True, cache=None, fold=True):
     """q [T, H, d], k [T, G, d], v [T, G, dv] as projected, through the cache writer (rotary, unit norms, the head mix folded
     into the queries) and an attention kernel; pages of the slot in reverse order in a pool whose other lines hold garbage."""
     from dllama_b200.models.layered import rotary_frequencies
@@ -146,7 +146,8 @@ def _attention_rows(q, k, v, talk, scale, rot, base, ctype, tc=False, portions=N
         if tc:
             rq = L.talk_tc_rows(H, G, d, dv, G, n)          # tiles of 16, 64 or 128 stacked (row, head) pairs by the portion's length
             tiles = [list(range(i, min(i + rq, n))) for i in range(0, n, rq)]
-            L.talk_attention_tiles(qm, o, H, G, d, dv, scale, 0, pos, slot, table, cache, tiles, rq, n_splits=n_splits, key_heads=G)
+            L.talk_attention_tiles(qm if fold else qq, o, H, G, d, dv, scale, 0, pos, slot, table, cache, tiles, rq, n_splits=n_splits,
+                                   key_heads=G if fold else 0)
         else:
             L.window_attention(qm, o, n, H, G, d, 0, scale, 0.0, 0, pos, slot, table, cache, vdim=dv, key_heads=G)
         out.append(o.cpu())
@@ -230,6 +231,43 @@ def test_head_mixed_attention_on_the_tensor_cores(H, G, d, dv, rot):
     want, _, _ = _mixed_want(q, k, v.bfloat16().float(), talk, scale, rot, 20000.0)
     for portions, n_splits in ((None, 1), ([(0, 36), (36, 2), (38, 1), (39, 59), (98, 102)], 3), ([(0, 199), (199, 1)], 16)):
         got, _ = _attention_rows(q, k, v, talk, scale, rot, 20000.0, torch.bfloat16, tc=True, portions=portions, n_splits=n_splits)
+        assert float((got - want).abs().max()) < 0.25, (portions, float((got - want).abs().max()))
+
+
+@pytest.mark.parametrize("H,G,d,dv,rot", [(6, 3, 24, 40, 16), (16, 4, 128, 128, 64), (8, 8, 32, 16, 0), (10, 2, 64, 80, 32)])
+def test_many_decoding_rows_share_one_staging_of_all_heads(H, G, d, dv, rot):
+    """Single rows of many sequences in one launch (here: 160 positions of one sequence as 160 one-row tiles with page
+    shares): enough CTAs for the form in which one CTA serves every key/value head of its tile."""
+    from dllama_b200.models.layered import rotary_frequencies
+    from dllama_b200.ops import layers as L
+    T, scale = 160, 12.0 / d
+    q, k, v, talk = _mixed_case(T, H, G, d, dv, seed=H + G)
+    want, _, _ = _mixed_want(q, k, v.bfloat16().float(), talk, scale, rot, 20000.0)
+    n_pages = T // PAGE
+    cache = (torch.randn(n_pages + 1, G, PAGE, d + dv, device="cuda") * 50).to(torch.bfloat16)
+    table = torch.tensor([list(range(n_pages, 0, -1))], dtype=torch.int32, device="cuda")
+    freqs = rotary_frequencies(20000.0, rot).cuda() if rot else torch.zeros(1, dtype=torch.float64, device="cuda")
+    pos, slot = torch.arange(T, dtype=torch.int32, device="cuda"), torch.zeros(T, dtype=torch.int32, device="cuda")
+    qq, kk, vv = (t.reshape(T, -1).float().cuda().contiguous() for t in (q, k, v))
+    qm, o = torch.zeros(T, H * G * d, device="cuda"), torch.zeros(T, H * dv, device="cuda")
+    L.window_kv_write(kk, T, G, d, rot, freqs, 1.0, pos, slot, table, cache, q=qq, q_heads=H, v=vv, vdim=dv, qk_norm=True, eps=1e-5,
+                      rope_half=True, talk=talk.cuda(), q_mixed=qm)
+    rq = L.talk_tc_rows(H, G, d, dv, G, 1)
+    assert rq * (H // G) <= 16
+    L.talk_attention_tiles(qm, o, H, G, d, dv, scale, 0, pos, slot, table, cache, [[i] for i in range(T)], rq, n_splits=4, key_heads=G)
+    got = o.cpu().double().reshape(T, H, dv)
+    assert float((got - want).abs().max()) < 0.25, float((got - want).abs().max())
+
+
+@pytest.mark.parametrize("H,G,d,dv", [(6, 3, 24, 40), (8, 2, 64, 80), (4, 1, 32, 8), (16, 8, 16, 104)])
+def test_the_tile_kernel_without_a_head_mix_is_plain_grouped_query_attention(H, G, d, dv):
+    """key_heads = 0: every head meets its own group's key; values of another width than the keys."""
+    T, scale = 130, 12.0 / d
+    q, k, v, _ = _mixed_case(T, H, G, d, dv, seed=H + dv)
+    eye = torch.eye(H)
+    want, _, _ = _mixed_want(q, k, v.bfloat16().float(), eye, scale, 8, 20000.0)
+    for portions, n_splits in ((None, 1), ([(0, 36), (36, 2), (38, 1), (39, 91)], 3), ([(0, 129), (129, 1)], 5)):
+        got, _ = _attention_rows(q, k, v, eye, scale, 8, 20000.0, torch.bfloat16, tc=True, portions=portions, n_splits=n_splits, fold=False)
         assert float((got - want).abs().max()) < 0.25, (portions, float((got - want).abs().max()))
 
 
