@@ -275,13 +275,9 @@ __global__ void __launch_bounds__(128) talk_merge_kernel(DlWindowAttnArgs a, con
     for (int idx = threadIdx.x; idx < rep * DV; idx += blockDim.x) {
         const int hg = idx / DV, c = idx - hg * DV;
         const float* p = base + (size_t)(r * rep + hg) * (DVP + 2) + c;
-        float acc = 0.f;                      // shares that weigh nothing (no visible key in their pages) are not read; the other loads go out together
-#pragma unroll 4
-        for (int k = 0; k < n_splits; ++k) {
-            const float w = w_s[hg * n_splits + k];
-            const float v = w != 0.f ? p[(size_t)k * TA_ROWS * (DVP + 2)] : 0.f;
-            acc = fmaf(w, v, acc);
-        }
+        float acc = 0.f;                      // a share without pages left zeros and weighs 0: every load can go out at once
+#pragma unroll 8
+        for (int k = 0; k < n_splits; ++k) acc = fmaf(w_s[hg * n_splits + k], p[(size_t)k * TA_ROWS * (DVP + 2)], acc);
         a.out[(size_t)m * a.ldo + (size_t)(g * rep + hg) * DV + c] = acc;
     }
 }

@@ -513,7 +513,8 @@ class WindowAttentionMixer:
             span = self.window or self.chunk
             pages = (span + PAGE - 1) // PAGE + 1 if span else e.max_pages
             n_splits = 1
-            if n_tiles * G <= 2 * e.n_sms:
+            # the tall tiles of long portions fill the SMs from one CTA each (page shares only add their merge: measured)
+            if n_tiles * G <= (e.n_sms - 1 if self.tc_talk and rq > self.tc_rq_small else 2 * e.n_sms):
                 n_splits = max(1, min(pages, WINDOW_MAX_SPLITS, (WINDOW_CTAS_PER_SM * e.n_sms) // (n_tiles * G)))
             partial = e.window_partial(d, self.partial_floats) if n_splits > 1 else None
             if self.tc_talk:
