@@ -57,8 +57,10 @@ __global__ void __launch_bounds__((NR == 8 || ALLG) ? 256 : 128) talk_attention_
     __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][TA_PAGE][LDS]
     __nv_bfloat16* q_s = kv_s + (size_t)2 * TA_PAGE * LDS;                          // [TA_ROWS (ALLG: per key/value head)][QS]: the stacked queries
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
-    const int tile = blockIdx.x, rep = a.heads / a.kv_heads;
-    const int g = ALLG ? min(warp, a.kv_heads - 1) : (int)blockIdx.y;              // ALLG: warp g multiplies key/value head g
+    // grid (key/value heads, tiles, page shares).  A sequence's later tiles walk more pages: they start first, so that the
+    // short ones fill the SMs at the end
+    const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, rep = a.heads / a.kv_heads;
+    const int g = ALLG ? min(warp, a.kv_heads - 1) : (int)blockIdx.x;              // ALLG: warp g multiplies key/value head g
     const int wrow = ALLG ? 0 : warp;                                               // this warp's block of 16 stacked rows among its group's
     const int qrow0 = ALLG ? g * 16 : warp * 16;                                    // ... and where that block's queries sit in q_s
     if (threadIdx.x < rq) s_row[threadIdx.x] = tile_rows[(size_t)tile * rq + threadIdx.x];
@@ -334,7 +336,7 @@ static int launch_talk_nr(const DlWindowAttnArgs& a, const int* tile_rows, int n
         cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<DK, NV, NR, ALLG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { dl_set_error("dl_talk_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
     }
-    const dim3 grid(n_tiles, ALLG ? 1 : a.kv_heads, n_splits);
+    const dim3 grid(ALLG ? 1 : a.kv_heads, n_tiles, n_splits);
     const int threads = ALLG ? (a.kv_heads > 4 ? 256 : 128) : (NR == 8 ? 256 : 128);
     talk_attention_mma_kernel<DK, NV, NR, ALLG><<<grid, threads, smem, st>>>(a, tile_rows, rq, n_splits, partial);
     return 0;
@@ -365,6 +367,7 @@ extern "C" int dl_talk_attention_tc(const DlWindowAttnArgs* args, const int* til
         return -1;
     }
     if (n_tiles < 1) return 0;
+    if (n_tiles > 65535) { dl_set_error("dl_talk_attention_tc: %d tiles in one launch", n_tiles); return -1; }
     if (n_splits < 1 || n_splits > TA_MAX_SPLITS || (n_splits > 1 && partial == nullptr)) { dl_set_error("dl_talk_attention_tc: n_splits %d without scratch", n_splits); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     const int dk = ta_dk(a.dim), nv = ta_nv(a.vdim);

@@ -99,9 +99,10 @@ def talk_attention(a):
     qm = torch.zeros(n, H * G * d, device="cuda")
     pos, slot = torch.arange(n, dtype=torch.int32).cuda(), torch.zeros(n, dtype=torch.int32).cuda()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    freqs = rotary_frequencies(500000.0, rd).cuda()
     for _ in range(3):
         ev0.record()
-        L.window_kv_write(k, n, G, d, rd, rotary_frequencies(500000.0, rd).cuda(), 1.0, pos, slot, bt, cache, q=q, q_heads=H, v=v, vdim=dv,
+        L.window_kv_write(k, n, G, d, rd, freqs, 1.0, pos, slot, bt, cache, q=q, q_heads=H, v=v, vdim=dv,
                           qk_norm=True, eps=1e-5, rope_half=True, talk=talk, q_mixed=qm)
         ev1.record()
         torch.cuda.synchronize()
