@@ -107,20 +107,20 @@ __global__ void __launch_bounds__((NR == 8 || ALLG) ? 256 : 128) talk_attention_
     for (int v = 0; v < NV; ++v) { o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const int kch = D / 8, vch = DV / 8, per_line = KS * kch + VS * vch;
+    // staging: THREADS / 32 threads share a cache line's chunks of 16 bytes, head after head (no index arithmetic per chunk)
+    const int kch = D / 8, vch = DV / 8, TPL = THREADS / TA_PAGE;
+    const int sj = threadIdx.x / TPL, sl = threadIdx.x - sj * TPL;                  // this thread's line of a page and its lane among the line's threads
     auto issue = [&](int pg, int buf) {
         const int page = a.block_table[(size_t)slot * a.max_pages + pg];
-        const __nv_bfloat16* src0 = (const __nv_bfloat16*)a.cache + (size_t)page * a.kv_heads * TA_PAGE * LD;
-        __nv_bfloat16* dst = kv_s + (size_t)buf * TA_PAGE * LDS;
-        for (int i = threadIdx.x; i < TA_PAGE * per_line; i += THREADS) {
-            const int j = i / per_line, part = i - j * per_line;
-            if (part < KS * kch) {
-                const int c = part / kch, p = part - c * kch;
-                cp_async16(dst + (size_t)j * LDS + c * DP + p * 8, src0 + ((size_t)(KS > 1 ? c : g) * TA_PAGE + j) * LD + p * 8);
-            } else {
-                const int c = (part - KS * kch) / vch, p = part - KS * kch - c * vch;
-                cp_async16(dst + (size_t)j * LDS + VOFF + c * DVP + p * 8, src0 + ((size_t)(ALLG ? c : g) * TA_PAGE + j) * LD + D + p * 8);
-            }
+        const __nv_bfloat16* src0 = (const __nv_bfloat16*)a.cache + ((size_t)page * a.kv_heads * TA_PAGE + sj) * LD;      // head c: + c * TA_PAGE * LD
+        __nv_bfloat16* dst = kv_s + (size_t)buf * TA_PAGE * LDS + (size_t)sj * LDS;
+        for (int c = 0; c < KS; ++c) {
+            const __nv_bfloat16* sk = src0 + (size_t)(KS > 1 ? c : g) * TA_PAGE * LD;
+            for (int p = sl; p < kch; p += TPL) cp_async16(dst + c * DP + p * 8, sk + p * 8);
+        }
+        for (int c = 0; c < VS; ++c) {
+            const __nv_bfloat16* sv = src0 + (size_t)(ALLG ? c : g) * TA_PAGE * LD + D;
+            for (int p = sl; p < vch; p += TPL) cp_async16(dst + VOFF + c * DVP + p * 8, sv + p * 8);
         }
     };
     if (pg_lo <= pg_hi) issue(pg_lo, 0);
