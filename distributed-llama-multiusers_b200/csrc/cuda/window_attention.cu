@@ -144,11 +144,16 @@ __global__ void __launch_bounds__(256) attn_kv_write_kernel(DlWindowKvArgs a) {
         __syncthreads();
         const int rep = nq / a.kv_heads, QD = a.kv_heads * D;
         const float* qs = heads_s + (size_t)a.kv_heads * D;
-        for (int t = threadIdx.x; t < nq * QD; t += blockDim.x) {
-            const int h = t / QD, c = (t - h * QD) / D, i = t - h * QD - c * D;
-            float acc = 0.f;
-            for (int g = c * rep; g < (c + 1) * rep; ++g) acc = fmaf(talk_s[h * nq + g], qs[(size_t)g * D + i], acc);
-            a.q_mixed[(size_t)m * a.ld_qm + t] = acc;
+        float* out = a.q_mixed + (size_t)m * a.ld_qm;
+        for (int t = threadIdx.x; t < QD; t += blockDim.x) {      // a thread owns column t = c * D + i of every head's folded query
+            const int c = t / D, i = t - c * D;
+            const float* qc = qs + (size_t)c * rep * D + i;
+            for (int h = 0; h < nq; ++h) {
+                const float* tk = talk_s + h * nq + c * rep;
+                float acc = 0.f;
+                for (int g = 0; g < rep; ++g) acc = fmaf(tk[g], qc[(size_t)g * D], acc);
+                out[(size_t)h * QD + t] = acc;
+            }
         }
     }
 }
